@@ -9,7 +9,8 @@ however many layers there are (the reference keeps one table per layer,
 include/backend/kvcache/block_pool.hpp:73-103).  Groups with a window give pages back as soon
 as the window has passed them; everything is given back when a request is closed.
 
-Device layout of a group: ``[num_pages + 1, calls, 2 (k|v), kv_heads, page_size, head_dim]``.
+Device layout of a group: ``[num_pages + 1, calls, planes, kv_heads, page_size, head_dim]``; the usual cache has two
+planes (keys, values), a cache whose rows are keys and values at once (the latent of a latent-attention layer) has one.
 The extra last page is a scratch page that is never handed out: padding tokens of a
 captured decode step write there.
 """
@@ -29,6 +30,7 @@ class PagedKVNeed:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None        # None: all keys; else the last `window` keys
+    planes: int = 2                     # 2: keys and values; 1: one row per token that serves as both (a latent)
 
 
 @dataclass(frozen=True)
@@ -44,7 +46,7 @@ class CallCacheView:
     group: int = -1                     # paged: index of the group (selects the block table)
     tensor: Optional[torch.Tensor] = None   # paged: this call's slice of the pool; state: [slots, *shape]
     page_stride: int = 0                # elements between pages
-    kv_stride: int = 0                  # elements between the k and the v half of a page
+    kv_stride: int = 0                  # elements between the k and the v half of a page (0: one plane serves as both)
     page_size: int = 0
     window: Optional[int] = None
 
@@ -54,13 +56,14 @@ class PagedGroup:
     n_kv_heads: int
     head_dim: int
     window: Optional[int]
+    planes: int = 2
     calls: List[int] = field(default_factory=list)
     pool: Optional[PagePool] = None
     tensor: Optional[torch.Tensor] = None
     num_pages: int = 0                  # pages of this group's pool; page ``num_pages`` of the tensor is the scratch page
 
     def page_elems(self, page_size: int) -> int:
-        return len(self.calls) * 2 * self.n_kv_heads * page_size * self.head_dim
+        return len(self.calls) * self.planes * self.n_kv_heads * page_size * self.head_dim
 
 
 class RequestCache:
@@ -102,11 +105,13 @@ class CacheManager:
                 continue
             if isinstance(need, PagedKVNeed):
                 for gi, g in enumerate(self.groups):
-                    if (g.n_kv_heads, g.head_dim, g.window) == (need.n_kv_heads, need.head_dim, need.window):
+                    if (g.n_kv_heads, g.head_dim, g.window, g.planes) == (need.n_kv_heads, need.head_dim, need.window, need.planes):
                         break
                 else:
+                    if need.planes not in (1, 2):
+                        raise ValueError(f"call {call}: a paged cache has 1 or 2 planes, not {need.planes}")
                     gi = len(self.groups)
-                    self.groups.append(PagedGroup(need.n_kv_heads, need.head_dim, need.window))
+                    self.groups.append(PagedGroup(need.n_kv_heads, need.head_dim, need.window, need.planes))
                 self._call_group[call] = (gi, len(self.groups[gi].calls))
                 self.groups[gi].calls.append(call)
             elif isinstance(need, StateNeed):
@@ -179,7 +184,7 @@ class CacheManager:
         self.device, self.dtype = torch.device(device), dtype
         for g in self.groups:
             # zeroed: attention multiplies slots that hold nothing yet by probability 0, which must not meet NaN bits
-            g.tensor = torch.zeros((g.num_pages + 1, len(g.calls), 2, g.n_kv_heads, self.page_size, g.head_dim),
+            g.tensor = torch.zeros((g.num_pages + 1, len(g.calls), g.planes, g.n_kv_heads, self.page_size, g.head_dim),
                                    dtype=dtype, device=device)
         for call, need in self._state_needs.items():
             self._state_tensors[call] = torch.zeros((self.max_requests,) + tuple(need.shape), dtype=need.dtype,
@@ -206,7 +211,7 @@ class CacheManager:
             t = g.tensor[:, j] if g.tensor is not None else None
             return CallCacheView("paged", gi, t,
                                  page_stride=g.page_elems(self.page_size),
-                                 kv_stride=g.n_kv_heads * self.page_size * g.head_dim,
+                                 kv_stride=g.n_kv_heads * self.page_size * g.head_dim if g.planes == 2 else 0,
                                  page_size=self.page_size, window=g.window)
         if call in self._state_needs:
             return CallCacheView("state", tensor=self._state_tensors.get(call))

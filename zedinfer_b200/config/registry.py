@@ -56,9 +56,10 @@ def _load_builtin() -> None:
 
 
 def resolve_architecture(raw: Mapping[str, Any]) -> Architecture:
-    """Pick the architecture for a config dict: ``architectures[0]``, else ``model_type``."""
+    """Pick the architecture for a config dict: ``architectures[0]`` (or the single name under ``architecture``), else
+    ``model_type``."""
     _load_builtin()
-    names = raw.get("architectures") or []
+    names = raw.get("architectures") or raw.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     for n in names:

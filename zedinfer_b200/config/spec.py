@@ -49,6 +49,7 @@ class LayerSpec:
     norms: Mapping[str, PartSpec]
     prefixes: Mapping[str, str]
     extra: Mapping[str, Tuple[str, PartSpec]] = field(default_factory=dict)
+    block_params: Mapping[str, Any] = field(default_factory=dict)     # constants of the arrangement itself
 
     def part_specs(self) -> Tuple[Tuple[str, str, PartSpec], ...]:
         """(role, family, spec) of every part of the layer, in a fixed order."""

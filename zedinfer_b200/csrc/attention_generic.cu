@@ -1,5 +1,5 @@
 // Paged causal attention, one warp per (query token, query head); float32 or bfloat16 storage,
-// float32 arithmetic.  Takes any head_dim that is a multiple of 8 up to 256, any number of
+// float32 arithmetic.  Takes any head_dim that is a multiple of 8 up to 512, any number of
 // heads and groups, any page size, and an optional window.
 //
 // This kernel is the whole 32-bit path and the general fallback of the bfloat16 path.  A query
@@ -10,20 +10,24 @@
 //
 // Cache addressing (one call's slice of the pool): element (page, kv, kvh, off, d) lives at
 //   cache + page*page_stride + kv*kv_stride + (kvh*page_size + off)*head_dim + d.
+// kv_stride = 0: a cache with one plane, whose rows are keys and values at once (a latent).
+//
+// sinks (optional, float32 per query head): the softmax's denominator also holds exp(sinks[h]), a term with no
+// key and no value; it is added once, after the last tile, relative to the running maximum of the scores.
 #include "zi_common.cuh"
 
 ZI_DEFINE_LAST_ERROR(attention_generic)
 
 #define WARPS 4
-#define MAX_DREG 8            // head_dim <= 256
+// A lane keeps head_dim / 32 output elements: 8 registers up to head_dim 256, 16 up to 512.
 
-template <typename T>
+template <typename T, int MAX_DREG>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, T* __restrict__ out,
                        const int* __restrict__ tables, const int* __restrict__ tok_seg,
                        const int* __restrict__ pos, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                        int page_size, int max_blocks, long long page_stride, long long kv_stride, int window,
-                       float scale) {
+                       float scale, const float* __restrict__ sinks) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* qs = smem + warp * head_dim;                                     // this warp's query
@@ -83,6 +87,7 @@ paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, T* 
         }
         __syncwarp();
     }
+    if (sinks) l += expf(sinks[h] - m);
     const float inv = 1.0f / l;
     T* orow = out + ((size_t)n * n_heads + h) * head_dim;
 #pragma unroll
@@ -95,10 +100,11 @@ paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, T* 
 ZI_EXPORT int zi_paged_attention(const void* q, const void* cache, void* out, int dtype, const int* tables,
                                  const int* tok_seg, const int* pos, int n_tokens, int n_heads, int n_kv_heads,
                                  int head_dim, int page_size, int max_blocks, long long page_stride,
-                                 long long kv_stride, int window, float scale, cudaStream_t stream) {
+                                 long long kv_stride, int window, float scale, const float* sinks,
+                                 cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (head_dim <= 0 || head_dim % 8 != 0 || head_dim > 32 * MAX_DREG)
-        return zi_fail("attention: head_dim=%d must be a multiple of 8 and at most %d", head_dim, 32 * MAX_DREG);
+    if (head_dim <= 0 || head_dim % 8 != 0 || head_dim > 512)
+        return zi_fail("attention: head_dim=%d must be a multiple of 8 and at most %d", head_dim, 512);
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         return zi_fail("attention: %d query heads cannot share %d key/value heads", n_heads, n_kv_heads);
     if (page_size <= 0 || max_blocks <= 0) return zi_fail("attention: page_size=%d max_blocks=%d", page_size, max_blocks);
@@ -107,9 +113,14 @@ ZI_EXPORT int zi_paged_attention(const void* q, const void* cache, void* out, in
     if (blocks > 0x7fffffffLL) return zi_fail("attention: too many (token, head) pairs: %lld", items);
     const size_t smem = (size_t)WARPS * head_dim * sizeof(float) + (size_t)WARPS * 32 * sizeof(long long);
     ZI_DISPATCH(dtype, T, {
-        paged_attention_kernel<T><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(
-            (const T*)q, (const T*)cache, (T*)out, tables, tok_seg, pos, n_tokens, n_heads, n_kv_heads, head_dim,
-            page_size, max_blocks, page_stride, kv_stride, window, scale);
+        if (head_dim <= 256)
+            paged_attention_kernel<T, 8><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(
+                (const T*)q, (const T*)cache, (T*)out, tables, tok_seg, pos, n_tokens, n_heads, n_kv_heads, head_dim,
+                page_size, max_blocks, page_stride, kv_stride, window, scale, sinks);
+        else
+            paged_attention_kernel<T, 16><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(
+                (const T*)q, (const T*)cache, (T*)out, tables, tok_seg, pos, n_tokens, n_heads, n_kv_heads, head_dim,
+                page_size, max_blocks, page_stride, kv_stride, window, scale, sinks);
     });
     return zi_check_launch("paged_attention");
 }

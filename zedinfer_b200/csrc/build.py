@@ -42,6 +42,8 @@ SOURCES: Dict[str, str] = {
     "gemm_smallm": "gemm_smallm.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_tcgen05": "attention_tcgen05.cu",
+    "rowwise": "rowwise.cu",
+    "moe": "moe.cu",
 }
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 EXTRA_LIBS: Dict[str, List[str]] = {}

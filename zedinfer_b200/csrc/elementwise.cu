@@ -36,8 +36,8 @@ ZI_EXPORT int zi_embedding(const void* table, int table_dtype, const int* ids, v
 
 // ---------------------------------------------------------------------------------------
 // RMSNorm.  y = (w * x) * rstd, rstd = 1/sqrt(mean(x^2) + eps), all in float32.
-//   delta != null : x = residual[row] + delta[row] (float32 add); written back to residual
-//                   when write_residual is set.
+//   delta != null : x = residual[row] + delta_scale * delta[row] (one float32 fused multiply-add, which is the
+//                   plain float32 add when delta_scale is 1); written back to residual when write_residual is set.
 //   row_idx != null : output row r reads input row row_idx[r] (used for the rows whose
 //                   logits are wanted); the residual is then never written.
 // One block per output row, a fixed block size, so the sum's order is a function of the
@@ -67,7 +67,7 @@ template <typename TD, typename TW, typename TO>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const TW* __restrict__ w,
                TO* __restrict__ out, const int* __restrict__ row_idx, float eps, int hidden,
-               int write_residual) {
+               int write_residual, float delta_scale) {
     extern __shared__ float row[];           // hidden floats
     __shared__ float scratch[32];
     const int r = blockIdx.x;
@@ -79,7 +79,7 @@ rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const
     float ss = 0.0f;
     for (int j = threadIdx.x; j < hidden; j += NORM_THREADS) {
         float x = ld_dep(res + j);
-        if (d) x = x + ld_dep_f32<TD>(d + j);
+        if (d) x = fmaf(delta_scale, ld_dep_f32<TD>(d + j), x);
         row[j] = x;
         ss = fmaf(x, x, ss);
     }
@@ -102,7 +102,7 @@ template <typename TD, typename TW, typename TO>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_vec8_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const TW* __restrict__ w,
                     TO* __restrict__ out, const int* __restrict__ row_idx, float eps, int hidden,
-                    int write_residual) {
+                    int write_residual, float delta_scale) {
     extern __shared__ float row[];           // hidden floats
     __shared__ float scratch[32];
     const int r = blockIdx.x;
@@ -131,7 +131,7 @@ rmsnorm_vec8_kernel(float* __restrict__ residual, const TD* __restrict__ delta, 
                 float dv[8];
                 load8(d + j, dv);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) x[i] = x[i] + dv[i];
+                for (int i = 0; i < 8; ++i) x[i] = fmaf(delta_scale, dv[i], x[i]);
                 if (wb) store8(res + j, x);
             }
 #pragma unroll
@@ -154,7 +154,7 @@ rmsnorm_vec8_kernel(float* __restrict__ residual, const TD* __restrict__ delta, 
             float dv[8];
             load8(d + j, dv);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = x[i] + dv[i];
+            for (int i = 0; i < 8; ++i) x[i] = fmaf(delta_scale, dv[i], x[i]);
             if (wb) { if (keep) store8_hint(res + j, x, policy); else store8(res + j, x); }
         }
 #pragma unroll
@@ -182,7 +182,7 @@ template <typename TW, typename TO>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_parts_vec8_kernel(float* __restrict__ residual, const float* __restrict__ parts, int n_parts, long long part_stride,
                           const TW* __restrict__ w, TO* __restrict__ out, const int* __restrict__ row_idx, float eps,
-                          int hidden, int write_residual) {
+                          int hidden, int write_residual, float delta_scale) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
     const int r = blockIdx.x;
@@ -211,7 +211,7 @@ rmsnorm_parts_vec8_kernel(float* __restrict__ residual, const float* __restrict_
                 }
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = x[i] + to_f32<TO>(from_f32<TO>(dv[0][i]));
+            for (int i = 0; i < 8; ++i) x[i] = fmaf(delta_scale, to_f32<TO>(from_f32<TO>(dv[0][i])), x[i]);
             if (wb) store8(res + j, x);
 #pragma unroll
             for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
@@ -236,7 +236,7 @@ rmsnorm_parts_vec8_kernel(float* __restrict__ residual, const float* __restrict_
             for (int i = 0; i < 8; ++i) dv[i] += more[i];
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = x[i] + to_f32<TO>(from_f32<TO>(dv[i]));
+        for (int i = 0; i < 8; ++i) x[i] = fmaf(delta_scale, to_f32<TO>(from_f32<TO>(dv[i])), x[i]);
         if (wb) store8(res + j, x);
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
@@ -291,7 +291,7 @@ static int norm_smem_ok(int hidden, const void* fn) {
 // residual: float32 [*, hidden] (in/out).  delta: nullable, [*, hidden] of delta_dtype.
 ZI_EXPORT int zi_add_rmsnorm(void* residual, const void* delta, int delta_dtype, const void* w, int w_dtype,
                              void* out, int out_dtype, const int* row_idx, int rows, int hidden, float eps,
-                             int write_residual, cudaStream_t stream) {
+                             int write_residual, float delta_scale, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (hidden <= 0) return zi_fail("rmsnorm: width %d must be positive", hidden);
     const size_t smem = (size_t)hidden * sizeof(float);
@@ -300,7 +300,7 @@ ZI_EXPORT int zi_add_rmsnorm(void* residual, const void* delta, int delta_dtype,
         auto fn = vec ? rmsnorm_vec8_kernel<TD, TW, TO> : rmsnorm_kernel<TD, TW, TO>;
         if (norm_smem_ok(hidden, (const void*)fn)) return 1;
         zi_launch(fn, dim3(rows), dim3(NORM_THREADS), smem, stream, (float*)residual, (const TD*)delta, (const TW*)w,
-                  (TO*)out, row_idx, eps, hidden, (write_residual ? 1 : 0) | ((vec && rows <= NORM_FEW_ROWS) ? 2 : 0));
+                  (TO*)out, row_idx, eps, hidden, (write_residual ? 1 : 0) | ((vec && rows <= NORM_FEW_ROWS) ? 2 : 0), delta_scale);
     });););
     return zi_check_launch("add_rmsnorm");
 }
@@ -308,7 +308,7 @@ ZI_EXPORT int zi_add_rmsnorm(void* residual, const void* delta, int delta_dtype,
 // parts: float32 [n_parts][part_rows][hidden] (part_stride = part_rows * hidden elements); see rmsnorm_parts_vec8_kernel.
 ZI_EXPORT int zi_add_rmsnorm_parts(void* residual, const float* parts, int n_parts, long long part_stride, const void* w,
                                    int w_dtype, void* out, int out_dtype, const int* row_idx, int rows, int hidden, float eps,
-                                   int write_residual, cudaStream_t stream) {
+                                   int write_residual, float delta_scale, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (hidden <= 0 || hidden % 8) return zi_fail("rmsnorm: partial sums need a width that is a positive multiple of 8, got %d", hidden);
     if (n_parts < 1 || !parts) return zi_fail("rmsnorm: %d partial sums", n_parts);
@@ -319,7 +319,7 @@ ZI_EXPORT int zi_add_rmsnorm_parts(void* residual, const float* parts, int n_par
         auto fn = rmsnorm_parts_vec8_kernel<TW, TO>;
         if (norm_smem_ok(hidden, (const void*)fn)) return 1;
         fn<<<rows, NORM_THREADS, smem, stream>>>((float*)residual, parts, n_parts, part_stride, (const TW*)w, (TO*)out, row_idx,
-                                                  eps, hidden, (write_residual ? 1 : 0) | (rows <= NORM_FEW_ROWS ? 2 : 0));
+                                                  eps, hidden, (write_residual ? 1 : 0) | (rows <= NORM_FEW_ROWS ? 2 : 0), delta_scale);
     }););
     return zi_check_launch("add_rmsnorm_parts");
 }

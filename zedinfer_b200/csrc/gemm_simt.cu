@@ -18,7 +18,12 @@ ZI_DEFINE_LAST_ERROR(gemm_simt)
 template <typename TA, typename TW, typename TB, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_nt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const TB* __restrict__ bias,
-               TC* __restrict__ C, int M, int N, int K, long long lda, long long ldw, long long ldc) {
+               TC* __restrict__ C, int M, int N, int K, long long lda, long long ldw, long long ldc,
+               long long batch_a, long long batch_w, long long batch_c) {
+    // blockIdx.z: one product of a batch (operands and result `batch_*` elements apart; bias shared)
+    A += (size_t)blockIdx.z * batch_a;
+    W += (size_t)blockIdx.z * batch_w;
+    C += (size_t)blockIdx.z * batch_c;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -82,7 +87,24 @@ ZI_EXPORT int zi_gemm_nt(const void* A, int a_dtype, const void* W, int w_dtype,
     if (grid.y > 65535) return zi_fail("gemm: M=%d is too large for one launch", M);
     ZI_DISPATCH(a_dtype, TA, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(bias_dtype, TB, ZI_DISPATCH(c_dtype, TC, {
         gemm_nt_kernel<TA, TW, TB, TC><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (const TB*)bias, (TC*)C,
-                                                                 M, N, K, lda, ldw, ldc);
+                                                                 M, N, K, lda, ldw, ldc, 0, 0, 0);
     }););););
     return zi_check_launch("gemm_nt");
+}
+
+// A batch of such products in one launch: product b reads A + b*batch_a, W + b*batch_w and writes C + b*batch_c
+// (e.g. one product per attention head, heads interleaved in the rows of A and C).  No bias.
+ZI_EXPORT int zi_gemm_nt_batched(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype, int batch,
+                                 int M, int N, int K, long long lda, long long ldw, long long ldc, long long batch_a,
+                                 long long batch_w, long long batch_c, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    if (K <= 0) return zi_fail("gemm: K=%d must be positive", K);
+    if (lda < K || ldw < K || ldc < N) return zi_fail("gemm: leading dimensions (%lld, %lld, %lld) too small for K=%d N=%d", lda, ldw, ldc, K, N);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+    if (grid.y > 65535 || batch > 65535) return zi_fail("gemm: M=%d or batch=%d is too large for one launch", M, batch);
+    ZI_DISPATCH(a_dtype, TA, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(c_dtype, TC, {
+        gemm_nt_kernel<TA, TW, float, TC><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (const float*)nullptr, (TC*)C,
+                                                                    M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
+    });););
+    return zi_check_launch("gemm_nt_batched");
 }

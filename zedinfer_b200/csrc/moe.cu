@@ -1,0 +1,393 @@
+// Routed feed-forward (mixture of experts) on the device, without a trip to the host:
+//
+//   zi_route_topk     float32 router logits [n, E] -> the `top` largest per token (lowest index wins a tie) and the
+//                     softmax over those alone, in float32
+//   zi_moe_group      the (token, choice) pairs grouped by expert: offsets[E + 1], sorted row -> pair, pair -> sorted row
+//   zi_moe_gemm       grouped product: C[r, :] = A[src(r), :] . W[e(r)]^T for the sorted rows r of every expert, tiles
+//                     found on the device from the offsets; optional clamped, gated activation in the epilogue
+//   zi_moe_combine    out[t, :] = sum_j weight[t, j] * Y[row(t, j), :] (+ a shared expert's output), j in order
+//
+// A row's result depends on its own operands alone (one k-ascending chain per output element), so the order of rows
+// inside an expert's group, which comes from atomics, changes no value.
+#include "zi_common.cuh"
+#include <mma.h>
+
+ZI_DEFINE_LAST_ERROR(moe)
+
+// ---------------------------------------------------------------------------------------
+// Router: top-k and softmax over the chosen, one warp per token.
+// ---------------------------------------------------------------------------------------
+#define RT_WARPS 4
+#define RT_MAX_PER_LANE 32            // experts <= 1024
+__global__ void __launch_bounds__(RT_WARPS * 32)
+route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int* __restrict__ idx,
+                  float* __restrict__ wts) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * RT_WARPS + warp;
+    if (t >= n_tokens) return;
+    const float* z = logits + (size_t)t * n_experts;
+    float v[RT_MAX_PER_LANE];
+#pragma unroll
+    for (int i = 0; i < RT_MAX_PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = e < n_experts ? z[e] : -INFINITY;
+    }
+    float first = 0.0f, denom = 0.0f;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < RT_MAX_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < n_experts && (v[i] > best || (v[i] == best && e < best_e))) { best = v[i]; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (j == 0) first = best;                       // the largest of all: the softmax's reference point
+        const float p = expf(best - first);
+        denom += p;
+        if (lane == 0) { idx[(size_t)t * top + j] = best_e; wts[(size_t)t * top + j] = p; }
+#pragma unroll
+        for (int i = 0; i < RT_MAX_PER_LANE; ++i)
+            if (lane + 32 * i == best_e) v[i] = -INFINITY;
+    }
+    __syncwarp();
+    if (lane == 0)
+        for (int j = 0; j < top; ++j) wts[(size_t)t * top + j] = wts[(size_t)t * top + j] / denom;
+}
+
+ZI_EXPORT int zi_route_topk(const float* logits, int n_tokens, int n_experts, int top, int* idx, float* wts,
+                            cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_experts <= 0 || n_experts > 32 * RT_MAX_PER_LANE) return zi_fail("route_topk: %d experts (1..%d)", n_experts, 32 * RT_MAX_PER_LANE);
+    if (top <= 0 || top > n_experts) return zi_fail("route_topk: top=%d of %d experts", top, n_experts);
+    route_topk_kernel<<<(n_tokens + RT_WARPS - 1) / RT_WARPS, RT_WARPS * 32, 0, stream>>>(logits, n_tokens, n_experts, top, idx, wts);
+    return zi_check_launch("route_topk");
+}
+
+// ---------------------------------------------------------------------------------------
+// Grouping: one block.  offsets[e] .. offsets[e + 1] are the sorted rows of expert e.
+// ---------------------------------------------------------------------------------------
+#define GROUP_THREADS 1024
+__global__ void __launch_bounds__(GROUP_THREADS)
+moe_group_kernel(const int* __restrict__ idx, int n_pairs, int n_experts, int* __restrict__ offsets,
+                 int* __restrict__ row_pair, int* __restrict__ pair_row) {
+    extern __shared__ int sh[];                 // counts[E], then cursors[E]
+    int* counts = sh;
+    int* cursor = sh + n_experts;
+    for (int e = threadIdx.x; e < n_experts; e += GROUP_THREADS) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += GROUP_THREADS) atomicAdd(&counts[idx[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            offsets[e] = run;
+            cursor[e] = run;
+            run += counts[e];
+        }
+        offsets[n_experts] = run;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += GROUP_THREADS) {
+        const int r = atomicAdd(&cursor[idx[p]], 1);
+        row_pair[r] = p;
+        pair_row[p] = r;
+    }
+}
+
+ZI_EXPORT int zi_moe_group(const int* idx, int n_pairs, int n_experts, int* offsets, int* row_pair, int* pair_row,
+                           cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    if (n_experts <= 0 || n_experts > 4096) return zi_fail("moe_group: %d experts", n_experts);
+    moe_group_kernel<<<1, GROUP_THREADS, 2 * n_experts * sizeof(int), stream>>>(idx, n_pairs, n_experts, offsets, row_pair, pair_row);
+    return zi_check_launch("moe_group");
+}
+
+// ---------------------------------------------------------------------------------------
+// Grouped product.  Sorted row r belongs to expert e with offsets[e] <= r < offsets[e + 1]; its A row is
+// A[src, :] with src = row_pair[r] / pairs_per_src (row_pair null: src = r).  W is [E, N_w, K].
+//   gated == 0: C[r, n] = A[src] . W[e, n]                                  (N_w = N)
+//   gated == 1: W holds gate rows then up rows (N_w = 2 N);
+//               C[r, n] = act(A[src] . W[e, n], A[src] . W[e, N + n])       (see clamped_gate)
+// Block b walks the experts' tiles of TM rows: the block's (expert, first row) is found from the offsets.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float clamped_gate(float g, float u, float limit, float slope, float up_offset) {
+    if (limit > 0.0f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    return (g / (1.0f + expf(-slope * g))) * (u + up_offset);
+}
+
+__device__ __forceinline__ bool find_tile(const int* __restrict__ offsets, int n_experts, int tile, int tm, int* expert,
+                                          int* row0, int* row_end) {
+    int t = tile;
+    for (int e = 0; e < n_experts; ++e) {
+        const int lo = offsets[e], hi = offsets[e + 1];
+        const int tiles = (hi - lo + tm - 1) / tm;
+        if (t < tiles) {
+            *expert = e;
+            *row0 = lo + t * tm;
+            *row_end = hi;
+            return true;
+        }
+        t -= tiles;
+    }
+    return false;
+}
+
+// SIMT form: float32 FMA chains in rising k, any operand types (the whole 32-bit path, and bfloat16 shapes the
+// tensor-core form does not take).
+#define GM 32
+#define GN 64
+#define GK 16
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(256)
+moe_gemm_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ row_pair, int pairs_per_src,
+                     const TW* __restrict__ W, const int* __restrict__ offsets, int n_experts, TC* __restrict__ C,
+                     long long ldc, int N, int K, int gated, float limit, float slope, float up_offset) {
+    __shared__ float As[GK][GM + 1];
+    __shared__ float Ws[2][GK][GN + 1];
+    __shared__ int src_rows[GM];
+    __shared__ int tile_info[3];
+    if (threadIdx.x == 0) {
+        int e = 0, r0 = 0, rend = 0;
+        if (!find_tile(offsets, n_experts, blockIdx.y, GM, &e, &r0, &rend)) e = -1;
+        tile_info[0] = e; tile_info[1] = r0; tile_info[2] = rend;
+    }
+    __syncthreads();
+    const int e = tile_info[0], r0 = tile_info[1], rend = tile_info[2];
+    if (e < 0) return;
+    const int tid = threadIdx.x;
+    if (tid < GM) {
+        const int r = r0 + tid;
+        src_rows[tid] = r < rend ? (row_pair ? row_pair[r] / pairs_per_src : r) : -1;
+    }
+    __syncthreads();
+    const int n0 = blockIdx.x * GN;
+    const int n_w = gated ? 2 * N : N;
+    const TW* We = W + (size_t)e * n_w * K;
+    const int tx = tid & 15, ty = tid >> 4;          // 16 x 16 threads: 2 rows x 4 columns each
+    float acc[2][2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[h][i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += GK) {
+        // A tile: 32 rows x 16 k = 512 values, two per thread
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int i = tid * 2 + q, r = i / GK, k = k0 + i % GK;
+            const int src = src_rows[r];
+            As[i % GK][r] = (src >= 0 && k < K) ? to_f32<TA>(A[(size_t)src * lda + k]) : 0.0f;
+        }
+        // W tile(s): 64 rows x 16 k = 1024 values, four per thread
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int i = tid * 4 + q, r = i / GK, k = k0 + i % GK;
+            const int n = n0 + r;
+            const bool ok = n < N && k < K;
+            Ws[0][i % GK][r] = ok ? to_f32<TW>(We[(size_t)n * K + k]) : 0.0f;
+            if (gated) Ws[1][i % GK][r] = ok ? to_f32<TW>(We[(size_t)(N + n) * K + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GK; ++kk) {
+            float a[2], w[4];
+            a[0] = As[kk][ty * 2]; a[1] = As[kk][ty * 2 + 1];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = Ws[0][kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[0][i][j] = fmaf(a[i], w[j], acc[0][i][j]);
+            if (gated) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] = Ws[1][kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[1][i][j] = fmaf(a[i], w[j], acc[1][i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = r0 + ty * 2 + i;
+        if (r >= rend) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[0][i][j];
+            if (gated) {
+                // the two halves are rounded to the storage type first, as a separate product would have stored them
+                const float g = to_f32<TC>(from_f32<TC>(v)), u = to_f32<TC>(from_f32<TC>(acc[1][i][j]));
+                v = clamped_gate(g, u, limit, slope, up_offset);
+            }
+            C[(size_t)r * ldc + n] = from_f32<TC>(v);
+        }
+    }
+}
+
+// Tensor-core form (bfloat16 operands, float32 accumulation): 64 sorted rows x 64 columns per block, four warps of
+// 16 rows each, `wmma` 16x16x16 fragments; A rows gathered through the row map into shared memory, W rows read in
+// place.  K % 16 == 0 and 16-byte aligned rows.
+#define TM_ 64
+#define TN_ 64
+#define TK_ 32
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ row_pair, int pairs_per_src,
+                    const bf16* __restrict__ W, const int* __restrict__ offsets, int n_experts, bf16* C,
+                    long long ldc, int N, int K, int gated, float limit, float slope, float up_offset) {
+    using namespace nvcuda;
+    __shared__ __align__(32) bf16 As[TM_][TK_ + 8];
+    __shared__ __align__(32) bf16 Ws[2][TN_][TK_ + 8];
+    __shared__ __align__(32) float Cs[4][16][TN_ + 4];
+    __shared__ int src_rows[TM_];
+    __shared__ int tile_info[3];
+    if (threadIdx.x == 0) {
+        int e = 0, r0 = 0, rend = 0;
+        if (!find_tile(offsets, n_experts, blockIdx.y, TM_, &e, &r0, &rend)) e = -1;
+        tile_info[0] = e; tile_info[1] = r0; tile_info[2] = rend;
+    }
+    __syncthreads();
+    const int e = tile_info[0], r0 = tile_info[1], rend = tile_info[2];
+    if (e < 0) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < TM_) {
+        const int r = r0 + tid;
+        src_rows[tid] = r < rend ? (row_pair ? row_pair[r] / pairs_per_src : r) : -1;
+    }
+    __syncthreads();
+    const int n0 = blockIdx.x * TN_;
+    const int n_w = gated ? 2 * N : N;
+    const bf16* We = W + (size_t)e * n_w * K;
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[2][TN_ / 16];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < TN_ / 16; ++j) wmma::fill_fragment(acc[h][j], 0.0f);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int k0 = 0; k0 < K; k0 += TK_) {
+        // 64 rows x 32 k of A and of each W half: 256 pieces of 8 elements each, two per thread
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int i = tid * 2 + q, r = i >> 2, kc = (i & 3) * 8, k = k0 + kc;
+            const int src = src_rows[r];
+            *reinterpret_cast<uint4*>(&As[r][kc]) =
+                (src >= 0 && k < K) ? *reinterpret_cast<const uint4*>(A + (size_t)src * lda + k) : zero;
+            const int n = n0 + r;
+            const bool ok = n < N && k < K;
+            *reinterpret_cast<uint4*>(&Ws[0][r][kc]) = ok ? *reinterpret_cast<const uint4*>(We + (size_t)n * K + k) : zero;
+            if (gated)
+                *reinterpret_cast<uint4*>(&Ws[1][r][kc]) = ok ? *reinterpret_cast<const uint4*>(We + (size_t)(N + n) * K + k) : zero;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TK_; kk += 16) {
+            wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+            wmma::load_matrix_sync(a, &As[warp * 16][kk], TK_ + 8);
+#pragma unroll
+            for (int j = 0; j < TN_ / 16; ++j) {
+                wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b;
+                wmma::load_matrix_sync(b, &Ws[0][j * 16][kk], TK_ + 8);
+                wmma::mma_sync(acc[0][j], a, b, acc[0][j]);
+                if (gated) {
+                    wmma::load_matrix_sync(b, &Ws[1][j * 16][kk], TK_ + 8);
+                    wmma::mma_sync(acc[1][j], a, b, acc[1][j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // Epilogue through shared memory: each warp owns its 16 rows, a lane two columns of each.  With the activation
+    // the up half goes first and is parked, rounded to the storage type, in the output element it belongs to; the
+    // same thread reads it back when the gate half follows.
+    for (int h = gated ? 1 : 0; h >= 0; --h) {
+#pragma unroll
+        for (int j = 0; j < TN_ / 16; ++j) wmma::store_matrix_sync(&Cs[warp][0][j * 16], acc[h][j], TN_ + 4, wmma::mem_row_major);
+        __syncwarp();
+        for (int rr = 0; rr < 16; ++rr) {
+            const int r = r0 + warp * 16 + rr;
+            if (r >= rend) break;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int col = lane * 2 + c, n = n0 + col;
+                if (n >= N) continue;
+                bf16* dst = C + (size_t)r * ldc + n;
+                const float v = Cs[warp][rr][col];
+                if (h == 0 && gated) {
+                    const float g = to_f32<bf16>(from_f32<bf16>(v));
+                    *dst = from_f32<bf16>(clamped_gate(g, to_f32<bf16>(*dst), limit, slope, up_offset));
+                } else {
+                    *dst = from_f32<bf16>(v);
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
+ZI_EXPORT int zi_moe_gemm(const void* A, int a_dtype, long long lda, const int* row_pair, int pairs_per_src,
+                          const void* W, int w_dtype, const int* offsets, int n_experts, void* C, int c_dtype,
+                          long long ldc, int n_rows, int N, int K, int gated, float limit, float slope, float up_offset,
+                          int allow_tensor_cores, cudaStream_t stream) {
+    if (n_rows <= 0 || N <= 0) return 0;
+    if (K <= 0 || n_experts <= 0) return zi_fail("moe_gemm: K=%d experts=%d", K, n_experts);
+    if (row_pair && pairs_per_src <= 0) return zi_fail("moe_gemm: pairs_per_src=%d", pairs_per_src);
+    const bool tc = allow_tensor_cores && a_dtype == ZI_BF16 && w_dtype == ZI_BF16 && c_dtype == ZI_BF16 && K % 8 == 0 &&
+                    lda % 8 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0;
+    if (tc) {
+        dim3 grid((N + TN_ - 1) / TN_, (n_rows + TM_ - 1) / TM_ + n_experts);
+        if (grid.y > 65535) return zi_fail("moe_gemm: %d rows are too many for one launch", n_rows);
+        moe_gemm_mma_kernel<<<grid, 128, 0, stream>>>((const bf16*)A, lda, row_pair, pairs_per_src, (const bf16*)W, offsets,
+                                                      n_experts, (bf16*)C, ldc, N, K, gated, limit, slope, up_offset);
+        return zi_check_launch("moe_gemm");
+    }
+    dim3 grid((N + GN - 1) / GN, (n_rows + GM - 1) / GM + n_experts);
+    if (grid.y > 65535) return zi_fail("moe_gemm: %d rows are too many for one launch", n_rows);
+    ZI_DISPATCH(a_dtype, TA, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(c_dtype, TC, {
+        moe_gemm_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>((const TA*)A, lda, row_pair, pairs_per_src, (const TW*)W,
+                                                                  offsets, n_experts, (TC*)C, ldc, N, K, gated, limit, slope,
+                                                                  up_offset);
+    });););
+    return zi_check_launch("moe_gemm");
+}
+
+// ---------------------------------------------------------------------------------------
+// Combine: out[t, :] = sum_j wts[t, j] * Y[pair_row[t * top + j], :]  (+ shared[t, :]), j rising, float32, one rounding.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ Y, const int* __restrict__ pair_row, const float* __restrict__ wts,
+                                   const T* __restrict__ shared, T* __restrict__ out, int top, int hidden) {
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        float acc = 0.0f;
+        for (int c = 0; c < top; ++c) {
+            const int r = pair_row[(size_t)t * top + c];
+            acc = fmaf(wts[(size_t)t * top + c], to_f32<T>(Y[(size_t)r * hidden + j]), acc);
+        }
+        if (shared) acc += to_f32<T>(shared[(size_t)t * hidden + j]);
+        out[(size_t)t * hidden + j] = from_f32<T>(acc);
+    }
+}
+
+ZI_EXPORT int zi_moe_combine(const void* Y, const int* pair_row, const float* wts, const void* shared, void* out, int dtype,
+                             int n_tokens, int top, int hidden, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (top <= 0 || hidden <= 0) return zi_fail("moe_combine: top=%d hidden=%d", top, hidden);
+    ZI_DISPATCH(dtype, T, {
+        moe_combine_kernel<T><<<n_tokens, hidden >= 1024 ? 256 : 128, 0, stream>>>((const T*)Y, pair_row, wts, (const T*)shared,
+                                                                                  (T*)out, top, hidden);
+    });
+    return zi_check_launch("moe_combine");
+}

@@ -21,7 +21,8 @@ class Model:
         self.blocks: List[Block] = []
         for layer in spec.layers:
             cls = block_class(layer.block)
-            self.blocks.append(cls({role: build_part(family, ps) for role, family, ps in layer.part_specs()}))
+            self.blocks.append(cls({role: build_part(family, ps) for role, family, ps in layer.part_specs()},
+                                   **dict(layer.block_params)))
         # the caches of each call, by the role of the mixer they belong to: the key of the usual mixer's cache is
         # the index of the call that owns it, the key of any other mixer's cache is (that index, role)
         self._call_caches: List[Dict[str, object]] = []
@@ -103,7 +104,7 @@ class Model:
         """Run the step's tokens through every call; return float32 logits of ``logit_rows`` (or None)."""
         ctx.step_cache.clear()                 # what layers share (a step's rotation angles) belongs to one step
         h = torch.empty((ctx.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
-        self.embedding.forward(ctx.token_ids, h)
+        self.embedding.forward_step(ctx, h)
         stream = ResidualStream(h)
         if self._views_of is not cache_views:          # the same mapping step after step: resolve the keys once
             self._views_by_call = [{role: cache_views[key] for role, key in keys.items()} for keys in self._call_caches]

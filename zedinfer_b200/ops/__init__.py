@@ -26,10 +26,14 @@ _attention_mma = Library("attention_mma")
 _gemm_smallm = Library("gemm_smallm")
 _gemm_tcgen05 = Library("gemm_tcgen05")
 _attention_tcgen05 = Library("attention_tcgen05")
+_rowwise = Library("rowwise")
+_moe = Library("moe")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "rope_table", "gemm_smallm_rope", "can_fuse_rope_product", "silu_mul", "add", "cast",
-           "gemm_nt", "linear", "linear_for_residual", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode"]
+           "gemm_nt", "linear", "linear_for_residual", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode",
+           "embedding_positions", "softcap", "relu2", "gated_clamp_mul", "rmsnorm_append", "linear_per_head", "route_topk",
+           "moe_group", "moe_gemm", "moe_combine"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -54,8 +58,9 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> 
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, eps: float,
-                out: torch.Tensor, row_idx: Optional[torch.Tensor] = None, write_residual: bool = True) -> None:
-    """``residual (+= delta)``, then ``out = rmsnorm(residual) * w``.  ``residual`` is float32.
+                out: torch.Tensor, row_idx: Optional[torch.Tensor] = None, write_residual: bool = True,
+                delta_scale: float = 1.0) -> None:
+    """``residual (+= delta_scale * delta)``, then ``out = rmsnorm(residual) * w``.  ``residual`` is float32.
 
     With ``row_idx`` the output row ``r`` is computed from input row ``row_idx[r]`` and the
     residual is left untouched.
@@ -78,7 +83,7 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], w: torch.
         _elementwise.call("zi_add_rmsnorm_parts", ptr(residual), ptr(delta), c_int(delta.shape[0]),
                           c_ll(delta.shape[1] * hidden), ptr(w), c_int(dtype_code(w.dtype)), ptr(out),
                           c_int(dtype_code(out.dtype)), ptr(row_idx), c_int(rows), c_int(hidden), c_float(eps),
-                          c_int(1 if write_residual else 0), stream())
+                          c_int(1 if write_residual else 0), c_float(delta_scale), stream())
         return
     if delta is not None:
         need_contiguous("delta", delta)
@@ -94,7 +99,7 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], w: torch.
     _elementwise.call("zi_add_rmsnorm", ptr(residual), ptr(delta),
                       c_int(dtype_code(delta.dtype) if delta is not None else F32), ptr(w), c_int(dtype_code(w.dtype)),
                       ptr(out), c_int(dtype_code(out.dtype)), ptr(row_idx), c_int(rows), c_int(hidden), c_float(eps),
-                      c_int(1 if write_residual else 0), stream())
+                      c_int(1 if write_residual else 0), c_float(delta_scale), stream())
 
 
 ROPE_TABLE_MAX_TOKENS = 64       # steps of at most this many tokens rotate with the step's table of angles
@@ -508,9 +513,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
 
 def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                     tok_seg: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                    page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
-    """Causal attention of each token over its request's cache pages (general kernel)."""
-    need_cuda(q, cache, out, tables, tok_seg, pos)
+                    page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
+                    sinks: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of each token over its request's cache pages (general kernel).  ``kv_stride`` 0: the cache has
+    one plane whose rows are keys and values at once.  ``sinks``: float32, one per query head; ``exp(sinks[h])`` joins
+    the softmax's denominator (a term without key and value)."""
+    need_cuda(q, cache, out, tables, tok_seg, pos, sinks)
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads or not sinks.is_contiguous()):
+        raise KernelError(f"paged_attention: sinks must be contiguous float32 with {n_heads} entries")
     need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
     need_contiguous("q", q), need_contiguous("out", out)
     if q.dtype != cache.dtype or out.dtype != q.dtype:
@@ -519,7 +529,7 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tab
     _attention_generic.call("zi_paged_attention", ptr(q), ptr(cache), ptr(out), c_int(dtype_code(q.dtype)),
                             ptr(tables), ptr(tok_seg), ptr(pos), c_int(n), c_int(n_heads), c_int(n_kv_heads),
                             c_int(head_dim), c_int(page_size), c_int(tables.shape[1]), c_ll(page_stride),
-                            c_ll(kv_stride), c_int(window or 0), c_float(scale), stream())
+                            c_ll(kv_stride), c_int(window or 0), c_float(scale), ptr(sinks), stream())
 
 
 PREFILL_TILE_ROWS = 128          # query rows per entry of a step's tile list
@@ -621,7 +631,7 @@ def tcgen05_attention_ok(head_dim: int, page_size: int) -> bool:
 
 
 def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
-              window: Optional[int], scale: float) -> None:
+              window: Optional[int], scale: float, sinks: Optional[torch.Tensor] = None) -> None:
     """Attention of a step's tokens over the cache (``cache`` is a CallCacheView, ``ctx`` a StepContext).
 
     Picks a kernel by dtype and by the shape of the step; all of them compute the same function.
@@ -630,7 +640,7 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
     page sizes); float32 and other head sizes on the general kernel.
     """
     tables = ctx.tables[cache.group]
-    if q.dtype == torch.bfloat16 and head_dim in (64, 128):
+    if q.dtype == torch.bfloat16 and head_dim in (64, 128) and sinks is None and cache.kv_stride != 0:
         n = q.shape[0]
         if ctx.decode_only and tcgen05_attention_ok(head_dim, cache.page_size):
             # in a step of single tokens, token n is segment n
@@ -660,7 +670,7 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
                               cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
             return
     paged_attention(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads,
-                    head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+                    head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -749,3 +759,158 @@ def repetition_penalty(logits_row: torch.Tensor, tokens: torch.Tensor, penalty: 
         raise KernelError("repetition_penalty: one contiguous float32 row")
     _sampling.call("zi_repetition_penalty", ptr(logits_row), ptr(tokens), c_int(tokens.numel()),
                    c_int(logits_row.numel()), c_float(penalty), stream())
+
+
+# ---- row-wise kernels of csrc/rowwise.cu ---------------------------------------------------------------------------
+def embedding_positions(table: torch.Tensor, pos_table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
+                        out: torch.Tensor) -> None:
+    """``out[n] = table[ids[n]] + pos_table[positions[n]]``, added in float32."""
+    need_cuda(table, pos_table, ids, positions, out)
+    need_int32("ids", ids), need_int32("positions", positions)
+    need_contiguous("table", table), need_contiguous("pos_table", pos_table), need_contiguous("out", out)
+    need_contiguous("ids", ids), need_contiguous("positions", positions)
+    n, hidden = ids.numel(), table.shape[1]
+    if out.shape != (n, hidden) or pos_table.shape[1] != hidden or pos_table.dtype != table.dtype or positions.numel() != n:
+        raise KernelError(f"embedding_positions: table {tuple(table.shape)}, pos_table {tuple(pos_table.shape)}, "
+                          f"out {tuple(out.shape)} do not agree")
+    _rowwise.call("zi_embedding_pos", ptr(table), ptr(pos_table), c_int(dtype_code(table.dtype)), ptr(ids), ptr(positions),
+                  ptr(out), c_int(dtype_code(out.dtype)), c_int(n), c_int(hidden), c_int(table.shape[0]),
+                  c_int(pos_table.shape[0]), stream())
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """In place on float32: ``x = cap * tanh(x / cap)``."""
+    need_cuda(logits)
+    need_contiguous("logits", logits)
+    if logits.dtype != torch.float32:
+        raise KernelError("softcap: float32 only")
+    _rowwise.call("zi_softcap", ptr(logits), c_ll(logits.numel()), c_float(cap), stream())
+
+
+def relu2(x: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = max(x, 0)^2``."""
+    need_cuda(x, out)
+    need_contiguous("x", x), need_contiguous("out", out)
+    if x.shape != out.shape or x.dtype != out.dtype:
+        raise KernelError("relu2: x and out must agree")
+    _rowwise.call("zi_relu2", ptr(x), ptr(out), c_int(dtype_code(x.dtype)), c_ll(x.numel()), stream())
+
+
+def gated_clamp_mul(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, up_offset: float) -> None:
+    """``gate_up`` is ``[rows, 2 * I]`` (gate columns, then up columns): ``g = min(gate, limit)``, ``u = clamp(up,
+    -limit, limit)``, ``out = g * sigmoid(slope * g) * (u + up_offset)``.  ``limit <= 0``: no clamping."""
+    need_cuda(gate_up, out)
+    need_contiguous("gate_up", gate_up), need_contiguous("out", out)
+    rows, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (rows, two_i // 2) or out.dtype != gate_up.dtype:
+        raise KernelError(f"gated_clamp_mul: gate_up {tuple(gate_up.shape)} vs out {tuple(out.shape)}")
+    _rowwise.call("zi_gated_clamp_mul", ptr(gate_up), ptr(out), c_int(dtype_code(out.dtype)), c_int(rows), c_int(two_i // 2),
+                  c_float(limit), c_float(slope), c_float(up_offset), stream())
+
+
+def rmsnorm_append(x: torch.Tensor, w: torch.Tensor, eps: float, cache: torch.Tensor, tables: torch.Tensor,
+                   tok_seg: Optional[torch.Tensor], pos: torch.Tensor, page_size: int, page_stride: int) -> None:
+    """RMSNorm (plain weight) of every row of ``x`` (``[tokens, width]``, rows may be strided), written as the row of
+    its token in a paged cache with one plane and one head: page ``tables[tok_seg[n], pos[n] // page_size]``, offset
+    ``pos[n] % page_size``.  ``tok_seg`` None: token n is segment n."""
+    need_cuda(x, w, cache, tables, tok_seg, pos)
+    need_int32("tables", tables), need_int32("pos", pos)
+    if tok_seg is not None:
+        need_int32("tok_seg", tok_seg)
+    need_contiguous("w", w)
+    n, width = x.shape
+    if x.stride(1) != 1 or w.numel() != width:
+        raise KernelError(f"rmsnorm_append: x {tuple(x.shape)} strides {x.stride()}, w {tuple(w.shape)}")
+    _rowwise.call("zi_rmsnorm_append", ptr(x), c_int(dtype_code(x.dtype)), c_ll(x.stride(0)), ptr(w), c_int(dtype_code(w.dtype)),
+                  c_float(eps), ptr(cache), c_int(dtype_code(cache.dtype)), ptr(tables), ptr(tok_seg), ptr(pos), c_int(n),
+                  c_int(width), c_int(page_size), c_int(tables.shape[1]), c_ll(page_stride), stream())
+
+
+def linear_per_head(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """One product per head: ``out[n, h, :] = x[n, h, :] @ w[h].T`` with ``w [heads, N, K]`` and ``out [tokens, heads,
+    N]`` contiguous; ``x`` is ``[tokens, heads * K]`` (rows may be strided: a slice of a wider product's output) or
+    ``[tokens, heads, K]``.  bfloat16: one batched library product over strided views (float32 sums); any float32
+    operand: the SIMT kernel, one launch."""
+    need_cuda(x, w, out)
+    need_contiguous("w", w), need_contiguous("out", out)
+    heads, nn, k = w.shape
+    n = x.shape[0]
+    if x.dim() == 3:
+        need_contiguous("x", x)
+        x = x.view(n, heads * k)
+    if x.shape != (n, heads * k) or x.stride(1) != 1 or out.shape != (n, heads, nn):
+        raise KernelError(f"linear_per_head: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
+        xh = x.as_strided((heads, n, k), (k, x.stride(0), 1))
+        torch.bmm(xh, w.transpose(1, 2), out=out.transpose(0, 1))
+        return
+    _gemm_simt.call("zi_gemm_nt_batched", ptr(x), c_int(dtype_code(x.dtype)), ptr(w), c_int(dtype_code(w.dtype)), ptr(out),
+                    c_int(dtype_code(out.dtype)), c_int(heads), c_int(n), c_int(nn), c_int(k), c_ll(x.stride(0)), c_ll(k),
+                    c_ll(heads * nn), c_ll(k), c_ll(nn * k), c_ll(nn), stream())
+
+
+# ---- routed feed-forward, csrc/moe.cu ------------------------------------------------------------------------------
+def route_topk(logits: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor) -> None:
+    """Per row of float32 ``logits [tokens, experts]``: the ``top`` largest (lowest index wins a tie) into ``idx`` (int32
+    ``[tokens, top]``, largest first) and the softmax over those alone into ``wts`` (float32)."""
+    need_cuda(logits, idx, wts)
+    need_int32("idx", idx)
+    need_contiguous("logits", logits), need_contiguous("idx", idx), need_contiguous("wts", wts)
+    n, e = logits.shape
+    if logits.dtype != torch.float32 or wts.dtype != torch.float32 or idx.shape != (n, top) or wts.shape != (n, top):
+        raise KernelError(f"route_topk: logits {tuple(logits.shape)} {logits.dtype}, idx {tuple(idx.shape)}, wts {tuple(wts.shape)}")
+    _moe.call("zi_route_topk", ptr(logits), c_int(n), c_int(e), c_int(top), ptr(idx), ptr(wts), stream())
+
+
+def moe_group(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, row_pair: torch.Tensor, pair_row: torch.Tensor) -> None:
+    """Group the (token, choice) pairs of ``idx`` (int32 ``[tokens, top]``) by expert: ``offsets`` (int32
+    ``[experts + 1]``) bounds each expert's sorted rows, ``row_pair[r]`` is the pair at sorted row r and ``pair_row`` its
+    inverse."""
+    need_cuda(idx, offsets, row_pair, pair_row)
+    for name, t in (("idx", idx), ("offsets", offsets), ("row_pair", row_pair), ("pair_row", pair_row)):
+        need_int32(name, t), need_contiguous(name, t)
+    pairs = idx.numel()
+    if offsets.numel() != n_experts + 1 or row_pair.numel() != pairs or pair_row.numel() != pairs:
+        raise KernelError("moe_group: offsets [experts + 1], row_pair and pair_row one entry per pair")
+    _moe.call("zi_moe_group", ptr(idx), c_int(pairs), c_int(n_experts), ptr(offsets), ptr(row_pair), ptr(pair_row), stream())
+
+
+MOE_TENSOR_CORES = True          # bfloat16 grouped products on the tensor cores (False: the SIMT form, as float32 uses)
+
+
+def moe_gemm(a: torch.Tensor, row_pair: Optional[torch.Tensor], pairs_per_src: int, w: torch.Tensor, offsets: torch.Tensor,
+             out: torch.Tensor, gated: Optional[tuple] = None) -> None:
+    """Grouped product over the sorted rows of every expert: ``out[r] = a[src(r)] @ w[e(r)].T``; ``src(r) = row_pair[r]
+    // pairs_per_src`` (``row_pair`` None: r itself), ``e(r)`` from ``offsets``.  ``w`` is ``[experts, N, K]``, or with
+    ``gated = (limit, slope, up_offset)`` ``[experts, 2 N, K]`` (gate rows, then up rows) and ``out`` the clamped, gated
+    product of the two halves (see :func:`gated_clamp_mul`)."""
+    need_cuda(a, row_pair, w, offsets, out)
+    need_int32("offsets", offsets)
+    need_contiguous("w", w), need_contiguous("out", out)
+    if row_pair is not None:
+        need_int32("row_pair", row_pair)
+    rows, n = out.shape
+    e, n_w, k = w.shape
+    if a.stride(1) != 1 or a.shape[1] != k or n_w != (2 * n if gated else n) or offsets.numel() != e + 1:
+        raise KernelError(f"moe_gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+    limit, slope, up_offset = gated if gated else (0.0, 0.0, 0.0)
+    _moe.call("zi_moe_gemm", ptr(a), c_int(dtype_code(a.dtype)), c_ll(a.stride(0)), ptr(row_pair), c_int(pairs_per_src), ptr(w),
+              c_int(dtype_code(w.dtype)), ptr(offsets), c_int(e), ptr(out), c_int(dtype_code(out.dtype)), c_ll(out.stride(0)),
+              c_int(rows), c_int(n), c_int(k), c_int(1 if gated else 0), c_float(limit), c_float(slope), c_float(up_offset),
+              c_int(1 if MOE_TENSOR_CORES else 0), stream())
+
+
+def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, wts: torch.Tensor, shared: Optional[torch.Tensor],
+                out: torch.Tensor) -> None:
+    """``out[t] = sum_j wts[t, j] * y[pair_row[t, j]] (+ shared[t])``, j rising, in float32 with one rounding."""
+    need_cuda(y, pair_row, wts, shared, out)
+    need_int32("pair_row", pair_row)
+    need_contiguous("y", y), need_contiguous("pair_row", pair_row), need_contiguous("wts", wts), need_contiguous("out", out)
+    n, hidden = out.shape
+    top = wts.shape[1]
+    if wts.dtype != torch.float32 or wts.shape != (n, top) or pair_row.numel() != n * top or y.shape != (n * top, hidden) \
+            or y.dtype != out.dtype or (shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype
+                                                                or not shared.is_contiguous())):
+        raise KernelError(f"moe_combine: y {tuple(y.shape)}, wts {tuple(wts.shape)}, out {tuple(out.shape)} do not agree")
+    _moe.call("zi_moe_combine", ptr(y), ptr(pair_row), ptr(wts), ptr(shared), ptr(out), c_int(dtype_code(out.dtype)), c_int(n),
+              c_int(top), c_int(hidden), stream())

@@ -72,6 +72,7 @@ class ResidualStream:
     K was cut, ``ops.linear_for_residual``), which the norm that folds it adds in order and rounds to the step's type."""
     h: torch.Tensor
     delta: Optional[torch.Tensor] = None
+    delta_scale: float = 1.0     # the factor on ``delta`` when a norm folds it in: ``h += delta_scale * delta`` (float32)
 
 
 # ---- part interfaces ------------------------------------------------------------------------
@@ -108,6 +109,11 @@ class Embedding(Part):
 
     def forward(self, ids: torch.Tensor, out: torch.Tensor) -> None:
         raise NotImplementedError
+
+    def forward_step(self, ctx: "StepContext", out: torch.Tensor) -> None:
+        """What the model calls: an embedding that needs more of the step than its token ids (positions, segments)
+        overrides this; the default looks the ids up."""
+        self.forward(ctx.token_ids, out)
 
     def tied_weight(self) -> Optional[torch.Tensor]:
         return None
@@ -171,7 +177,10 @@ class Block:
     caches of the call by the role of the mixer they belong to (``caches["mixer"]`` for the usual one)."""
     capture_safe = False                  # see Part.capture_safe; an arrangement says so for its own code
 
-    def __init__(self, parts: Mapping[str, Part]):
+    def __init__(self, parts: Mapping[str, Part], **params: Any):
+        """``params``: the arrangement's own constants (``LayerSpec.block_params``); the base class takes none."""
+        if params:
+            raise TypeError(f"{type(self).__name__} takes no parameters, got {sorted(params)}")
         self._parts: Dict[str, Part] = dict(parts)
         self.mixer: Optional[Mixer] = self._parts.get("mixer")
         self.ffn: Optional[FeedForward] = self._parts.get("ffn")

@@ -3,7 +3,10 @@
     h = h + mixer(norm1(h));  h = h + ffn(norm2(h))
 
 The adds are fused into the norm that follows them: a branch output stays "pending" in the
-stream until the next norm folds it into the float32 residual."""
+stream until the next norm folds it into the float32 residual.
+
+``residual_scale`` m (default 1): ``h = h + m * mixer(norm1(h)); h = h + m * ffn(norm2(h))``, the product and the
+sum in float32.  A layer without a feed-forward (no ``ffn``, no ``norm2``) is its first half alone."""
 from __future__ import annotations
 
 from typing import Mapping
@@ -16,11 +19,13 @@ from .base import Block, ResidualStream, StepContext, register_block
 class PreNormBlock(Block):
     capture_safe = True
 
-    def __init__(self, parts):
+    def __init__(self, parts, residual_scale: float = 1.0):
         super().__init__(parts)
-        missing = [role for role in ("mixer", "ffn", "norm1", "norm2") if role not in self.parts()]
+        need = ("mixer", "norm1") + (("ffn", "norm2") if ("ffn" in self.parts() or "norm2" in self.parts()) else ())
+        missing = [role for role in need if role not in self.parts()]
         if missing:
             raise ValueError(f"the pre_norm arrangement needs the parts {missing} as well")
+        self.residual_scale = float(residual_scale)
 
     def forward(self, stream: ResidualStream, ctx: StepContext, caches: Mapping[str, CallCacheView],
                 owns_cache: bool) -> None:
@@ -28,6 +33,9 @@ class PreNormBlock(Block):
         normed = ctx.empty(n, hidden)
         self.norms["norm1"].forward_residual(stream, normed)
         stream.delta = self.mixer.forward_for_residual(normed, ctx, caches["mixer"], owns_cache)
+        stream.delta_scale = self.residual_scale
+        if self.ffn is None:
+            return
         normed2 = ctx.empty(n, hidden)
         self.norms["norm2"].forward_residual(stream, normed2)
         stream.delta = self.ffn.forward_for_residual(normed2, ctx)

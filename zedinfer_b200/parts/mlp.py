@@ -61,3 +61,81 @@ class GatedMLP(FeedForward):
 
     def forward_for_residual(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         return ops.linear_for_residual(self._activation(x, ctx), self.w_down, self.b_down)   # the product, or partial sums over K
+
+
+@register_feed_forward("squared_relu_mlp")
+class SquaredReluMLP(FeedForward):
+    """``down(relu(up(x))^2)``, no gate, no biases."""
+    capture_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, up_name: str = "up", down_name: str = "down"):
+        if hidden_size <= 0 or intermediate_size <= 0:
+            raise ValueError("squared_relu_mlp: sizes must be positive")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.up_name, self.down_name = up_name, down_name
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.up_name: TensorSpec((self.intermediate_size, self.hidden_size)),
+                self.down_name: TensorSpec((self.hidden_size, self.intermediate_size))}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_up = tensors[self.up_name].contiguous()
+        self.w_down = tensors[self.down_name].contiguous()
+
+    def _activation(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        act = ctx.empty(x.shape[0], self.intermediate_size)
+        ops.linear(x, self.w_up, None, act)
+        ops.relu2(act, act)
+        return act
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        out = ctx.empty(x.shape[0], self.hidden_size)
+        ops.linear(self._activation(x, ctx), self.w_down, None, out)
+        return out
+
+    def forward_for_residual(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return ops.linear_for_residual(self._activation(x, ctx), self.w_down, None)
+
+
+@register_feed_forward("clamped_gated_mlp")
+class ClampedGatedMLP(FeedForward):
+    """``down(g * sigmoid(slope * g) * (u + up_offset))`` with ``g = min(gate(x), limit)``, ``u = clamp(up(x), -limit,
+    limit)``; no biases.  ``limit=None``: no clamping."""
+    capture_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: Optional[float], slope: float = 1.0,
+                 up_offset: float = 0.0, gate_name: str = "gate", up_name: str = "up", down_name: str = "down"):
+        if hidden_size <= 0 or intermediate_size <= 0:
+            raise ValueError("clamped_gated_mlp: sizes must be positive")
+        if limit is not None and not limit > 0.0:
+            raise ValueError(f"clamped_gated_mlp: limit={limit} must be positive (or None)")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.limit, self.slope, self.up_offset = (float(limit) if limit is not None else 0.0), float(slope), float(up_offset)
+        self.gate_name, self.up_name, self.down_name = gate_name, up_name, down_name
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        h, i = self.hidden_size, self.intermediate_size
+        return {self.gate_name: TensorSpec((i, h)), self.up_name: TensorSpec((i, h)), self.down_name: TensorSpec((h, i))}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_gate_up = _stack([tensors[self.gate_name], tensors[self.up_name]])
+        self.w_down = tensors[self.down_name].contiguous()
+
+    def _activation(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        gate_up = ctx.empty(x.shape[0], 2 * self.intermediate_size)
+        ops.linear(x, self.w_gate_up, None, gate_up)
+        act = ctx.empty(x.shape[0], self.intermediate_size)
+        ops.gated_clamp_mul(gate_up, act, self.limit, self.slope, self.up_offset)
+        return act
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        out = ctx.empty(x.shape[0], self.hidden_size)
+        ops.linear(self._activation(x, ctx), self.w_down, None, out)
+        return out
+
+    def forward_for_residual(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return ops.linear_for_residual(self._activation(x, ctx), self.w_down, None)

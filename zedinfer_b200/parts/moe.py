@@ -1,0 +1,103 @@
+"""Routed feed-forward: every token runs ``top`` of ``experts`` small gated feed-forwards, weighted, plus an optional
+shared one that every token runs.
+
+    z = Wr x + b                     router logits, float32
+    S = the ``top`` largest z        (lowest index wins a tie)
+    y = sum_{e in S} softmax_S(z)_e * expert_e(x)   (+ shared(x))
+
+Each expert has the form of :class:`~zedinfer_b200.parts.mlp.ClampedGatedMLP`.  Nothing goes to the host: the step's
+(token, choice) pairs are grouped by expert on the device, the two products run as grouped products over the sorted
+rows (``csrc/moe.cu``; the activation in the first one's epilogue), and one kernel adds a token's rows with its router
+weights and the shared expert's output in float32.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from .. import ops
+from ..config.spec import PartSpec
+from ..weights.loader import TensorSpec
+from .base import FeedForward, StepContext, build_part, register_feed_forward
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, limit: Optional[float],
+                 slope: float = 1.0, up_offset: float = 0.0, router_bias: bool = True, shared: Optional[PartSpec] = None,
+                 expert_prefix: str = "e{e}.", router_name: str = "router", router_bias_name: str = "router.b",
+                 shared_prefix: str = "shared.", gate_name: str = "gate", up_name: str = "up", down_name: str = "down"):
+        """``shared``: the spec of a feed-forward that every token runs as well (its tensors under ``shared_prefix``)."""
+        if hidden_size <= 0 or intermediate_size <= 0:
+            raise ValueError("routed_experts: sizes must be positive")
+        if experts <= 0 or experts > 1024 or not 0 < top <= experts:
+            raise ValueError(f"routed_experts: top={top} of {experts} experts is not supported (1 <= top <= experts <= 1024)")
+        if limit is not None and not limit > 0.0:
+            raise ValueError(f"routed_experts: limit={limit} must be positive (or None)")
+        self.hidden_size, self.intermediate_size, self.experts, self.top = int(hidden_size), int(intermediate_size), int(experts), int(top)
+        self.limit, self.slope, self.up_offset = (float(limit) if limit is not None else 0.0), float(slope), float(up_offset)
+        self.router_bias = bool(router_bias)
+        self.expert_prefix, self.router_name, self.router_bias_name, self.shared_prefix = expert_prefix, router_name, router_bias_name, shared_prefix
+        self.gate_name, self.up_name, self.down_name = gate_name, up_name, down_name
+        self.shared = build_part("ffn", shared) if shared is not None else None
+        self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+
+    @property
+    def capture_safe(self) -> bool:
+        return self.shared is None or bool(getattr(self.shared, "capture_safe", False))
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        h, i = self.hidden_size, self.intermediate_size
+        specs = {self.router_name: TensorSpec((self.experts, h))}
+        if self.router_bias:
+            specs[self.router_bias_name] = TensorSpec((self.experts,))
+        for e in range(self.experts):
+            p = self.expert_prefix.format(e=e)
+            specs[p + self.gate_name] = TensorSpec((i, h))
+            specs[p + self.up_name] = TensorSpec((i, h))
+            specs[p + self.down_name] = TensorSpec((h, i))
+        if self.shared is not None:
+            for name, ts in self.shared.tensor_specs().items():
+                specs[self.shared_prefix + name] = ts
+        return specs
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_router = tensors[self.router_name].contiguous()
+        self.b_router = tensors[self.router_bias_name].float().contiguous() if self.router_bias else None
+        names = [self.expert_prefix.format(e=e) for e in range(self.experts)]
+        dtype = torch.float32 if any(tensors[p + n].dtype == torch.float32 for p in names
+                                     for n in (self.gate_name, self.up_name, self.down_name)) else tensors[names[0] + self.gate_name].dtype
+        # [experts, 2 * inner, hidden]: an expert's gate rows, then its up rows; [experts, hidden, inner]
+        self.w_gate_up = torch.stack([torch.cat([tensors[p + self.gate_name].to(dtype), tensors[p + self.up_name].to(dtype)], dim=0)
+                                      for p in names]).contiguous()
+        self.w_down = torch.stack([tensors[p + self.down_name].to(dtype) for p in names]).contiguous()
+        if self.shared is not None:
+            n = len(self.shared_prefix)
+            self.shared.bind({k[n:]: v for k, v in tensors.items() if k.startswith(self.shared_prefix)})
+
+    def route(self, x: torch.Tensor):
+        """(``idx`` int32 ``[tokens, top]``, ``wts`` float32 ``[tokens, top]``) of the step's tokens."""
+        n = x.shape[0]
+        logits = torch.empty((n, self.experts), dtype=torch.float32, device=x.device)
+        ops.gemm_nt(x, self.w_router, self.b_router, logits)             # float32 sums and result whatever the operands
+        idx = torch.empty((n, self.top), dtype=torch.int32, device=x.device)
+        wts = torch.empty((n, self.top), dtype=torch.float32, device=x.device)
+        ops.route_topk(logits, self.top, idx, wts)
+        return idx, wts
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        n, pairs = x.shape[0], x.shape[0] * self.top
+        idx, wts = self.route(x)
+        offsets = torch.empty(self.experts + 1, dtype=torch.int32, device=x.device)
+        row_pair = torch.empty(pairs, dtype=torch.int32, device=x.device)
+        pair_row = torch.empty(pairs, dtype=torch.int32, device=x.device)
+        ops.moe_group(idx, self.experts, offsets, row_pair, pair_row)
+        act = ctx.empty(pairs, self.intermediate_size)
+        ops.moe_gemm(x, row_pair, self.top, self.w_gate_up, offsets, act, gated=(self.limit, self.slope, self.up_offset))
+        y = ctx.empty(pairs, self.hidden_size)
+        ops.moe_gemm(act, None, 1, self.w_down, offsets, y)
+        shared = self.shared.forward(x, ctx) if self.shared is not None else None
+        out = ctx.empty(n, self.hidden_size)
+        ops.moe_combine(y, pair_row, wts, shared, out)
+        return out

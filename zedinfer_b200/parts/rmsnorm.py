@@ -1,5 +1,6 @@
 """RMSNorm: ``y = (w * x) * rstd``, ``rstd = 1 / sqrt(mean(x^2) + eps)``, in float32
-(src/backend/ops/rms_norm/cpu/rms_norm_cpu.cpp:24-28).  No ``+1`` on the weight."""
+(src/backend/ops/rms_norm/cpu/rms_norm_cpu.cpp:24-28).  No ``+1`` on the weight, unless the model stores its norm
+weights around zero (``unit_offset``): the factor is then ``1 + w``, formed once in float32 when the weight is bound."""
 from __future__ import annotations
 
 from typing import Dict, Mapping, Optional
@@ -15,19 +16,22 @@ from .base import Norm, ResidualStream, register_norm
 class RMSNorm(Norm):
     capture_safe = True
 
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, name: str = "weight", unit_offset: bool = False):
+        """``name``: the tensor's local name; ``unit_offset``: the stored weight is the factor's distance from one."""
         if size <= 0:
             raise ValueError(f"rmsnorm: size={size} must be positive")
         if not eps > 0.0:
             raise ValueError(f"rmsnorm: eps={eps} must be positive")
-        self.size, self.eps = int(size), float(eps)
+        self.size, self.eps, self.name, self.unit_offset = int(size), float(eps), str(name), bool(unit_offset)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.size,), init=("one_plus_normal", 0.01))}
+        return {self.name: TensorSpec((self.size,), init=("normal", 0.01) if self.unit_offset else ("one_plus_normal", 0.01))}
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        w = tensors[self.name]
+        # 1 + w does not fit bfloat16 without losing w's low bits: the factor is kept in float32 (the kernels take it so)
+        self.weight = (w.float() + 1.0).contiguous() if self.unit_offset else w.contiguous()
 
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
         ops.rmsnorm(x, self.weight, self.eps, out)
@@ -35,6 +39,6 @@ class RMSNorm(Norm):
     def forward_residual(self, stream: ResidualStream, out: torch.Tensor,
                          row_idx: Optional[torch.Tensor] = None) -> None:
         ops.add_rmsnorm(stream.h, stream.delta, self.weight, self.eps, out, row_idx=row_idx,
-                        write_residual=row_idx is None)
+                        write_residual=row_idx is None, delta_scale=stream.delta_scale)
         if row_idx is None:
             stream.delta = None
