@@ -292,6 +292,112 @@ def measure_head(core, cfg, rows, reps=20):
 REF_BENCH = os.path.join(ROOT, "baseline", "_ref", "ref_bench")
 
 
+# ---- the designs side by side ----------------------------------------------------------------------------------
+# `--designs`: prefill and decode of the Baselix design at layer sizes of real models, beside Qwen2 at equal size:
+# same width, layers, heads, head size, window, vocabulary and feed-forward weights per dense layer (Qwen2's gated
+# feed-forward has three matrices where the squared-ReLU one has two, so its inner width is two thirds).
+def baselix_config(width, heads, ff, window, layers, vocab, experts, top, expert_ff, shared_ff, rank=128, dim=128):
+    def mixer(kv_from=None):
+        m = {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": rank, "mask": {"size": window}, "scale": dim ** -0.5}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return m
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            out.append({"type": "latent_attention", "mixer": mixer(), "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            out.append({"type": "latent_attention", "mixer": mixer(i - 1),
+                        "mlp": {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
+                                "router": {"experts": experts, "top": top}, "shared": {"ff": shared_ff, "limit": 7.0}}})
+    return {"architecture": "Baselix", "vocab": vocab, "width": width, "max_positions": CONTEXT, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "logit_softcap": 30.0, "layers": out}
+
+
+def qwen2_config_like(width, heads, ff, window, layers, vocab, dim=128):
+    return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": layers, "hidden_size": width,
+            "num_attention_heads": heads, "num_key_value_heads": 2 if heads <= 12 else 4, "head_dim": dim,
+            "intermediate_size": (2 * ff // 3 + 7) // 8 * 8, "vocab_size": vocab, "rope_theta": 10000.0, "rms_norm_eps": 1e-6,
+            "tie_word_embeddings": True, "use_sliding_window": True, "sliding_window": window, "max_window_layers": 0,
+            "max_position_embeddings": CONTEXT, "torch_dtype": "bfloat16"}
+
+
+DESIGN_SIZES = {
+    "1.5b-class-layers": dict(width=1536, heads=12, ff=8960, window=1024, layers=8, vocab=32768, experts=16, top=4,
+                              expert_ff=1536, shared_ff=1536),
+    "4b-class-layers": dict(width=2560, heads=20, ff=13824, window=2048, layers=4, vocab=32768, experts=32, top=4,
+                            expert_ff=1792, shared_ff=3584),
+}
+
+
+def measure_design(cfg, vocab, batch, steps, warmup):
+    """Prefill of PROMPT_LEN tokens in one step and decode of `batch` requests through the captured greedy step."""
+    import torch
+    from zedinfer_b200.engine.core import EngineCore, StepEntry
+    core = EngineCore(None, "bfloat16", config=cfg, random_seed=SEED, page_size=PAGE_SIZE, max_tokens=(batch + 1) * CONTEXT,
+                      max_requests=batch, max_seq_len=CONTEXT, cuda_graphs=True)
+    prompts = random_prompts(3 + 5, PROMPT_LEN, vocab, SEED + 100)
+    times = []
+    for i, ids in enumerate(prompts):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        core.step([StepEntry(("p", i), ids, [PROMPT_LEN - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        core.end(("p", i))
+        if i >= 3:
+            times.append(a.elapsed_time(b))
+    prefill_ms = sum(times) / len(times)
+    dev = measure_decode_device(core, {"vocab_size": vocab}, batch, steps, warmup)
+    core.check_kernels()
+    weights = sum(t.numel() * t.element_size() for t in _model_tensors(core.model))
+    del core
+    torch.cuda.empty_cache()
+    return {"prefill_tokens_per_s": round(PROMPT_LEN / prefill_ms * 1000.0, 1), "prefill_ms": round(prefill_ms, 3),
+            "decode_tokens_per_s": round(dev["tok_s"], 1), "decode_ms_per_step": round(dev["ms"], 4),
+            "decode_launches_per_step": dev["launches"] // steps, "weight_bytes": weights}
+
+
+def _model_tensors(model):
+    seen, out = set(), []
+    for part, _ in model._part_prefixes():
+        for v in vars(part).values():
+            for t in (v if isinstance(v, (list, tuple)) else [v]):
+                if hasattr(t, "data_ptr") and t.data_ptr() not in seen:
+                    seen.add(t.data_ptr())
+                    out.append(t)
+            if hasattr(v, "tensor_specs") and hasattr(v, "__dict__"):         # a part inside a part (a shared expert)
+                for t in vars(v).values():
+                    if hasattr(t, "data_ptr") and t.data_ptr() not in seen:
+                        seen.add(t.data_ptr())
+                        out.append(t)
+    return out
+
+
+def design_comparison(args):
+    import torch  # noqa: F401
+    from zedinfer_b200.csrc import build
+    from zedinfer_b200.engine.core import EngineCore
+    build.compile_all(EngineCore.kernel_libraries("bfloat16") + ["gemm_tcgen05", "attention_tcgen05", "rowwise", "moe"], verbose=False)
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    clocks = ClockSampler()
+    clocks.start()
+    rows = []
+    for name, size in DESIGN_SIZES.items():
+        q = {k: size[k] for k in ("width", "heads", "ff", "window", "layers", "vocab")}
+        base = measure_design(baselix_config(**size), size["vocab"], args.batch, steps, warmup)
+        qwen = measure_design(qwen2_config_like(**q), size["vocab"], args.batch, steps, warmup)
+        rows.append({"size": name, "shape": size, "baselix": base, "qwen2_equal_size": qwen,
+                     "prefill_ratio": round(base["prefill_tokens_per_s"] / qwen["prefill_tokens_per_s"], 3),
+                     "decode_ratio": round(base["decode_tokens_per_s"] / qwen["decode_tokens_per_s"], 3)})
+    clocks.stop()
+    print(json.dumps({"metric": "designs_side_by_side", "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                      "dtype": "bf16", "data": "synthetic", "impl": "ours", "batch": args.batch, "prompt_len": PROMPT_LEN,
+                      "clocks": clocks.summary(), "designs": rows}))
+    return 0
+
+
 def decode_start(steps, warmup):
     mid = (PROMPT_LEN + CONTEXT) // 2
     return max(PROMPT_LEN, min(mid - steps // 2, CONTEXT - steps - warmup - 1))
@@ -379,6 +485,9 @@ def main():
     ap.add_argument("--layers", type=int, default=MODEL_1P5B["num_hidden_layers"],
                     help="fewer layers than the model has (same layer sizes), where memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the default workload: prefill and decode of the Baselix design at layer sizes of real "
+                         "models (random weights) beside Qwen2 at equal size")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -390,6 +499,8 @@ def main():
     if steps + warmup + 2 > CONTEXT - PROMPT_LEN:
         print(f"bench.py: --steps {steps} + --warmup {warmup} do not fit between the prompt and the context limit")
         return 2
+    if args.designs:
+        return design_comparison(args)
 
     import torch
     from zedinfer_b200.csrc import build

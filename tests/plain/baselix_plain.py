@@ -45,7 +45,8 @@ def read_safetensors(path: str, dtype=torch.float64) -> Dict[str, torch.Tensor]:
             continue
         b, e = info["data_offsets"]
         t = torch.frombuffer(bytearray(data[b:e]), dtype=kinds[info["dtype"]]).reshape(info["shape"])
-        out[name] = t.to(dtype) if t.is_floating_point() else t.clone()
+        key = name[6:] if name.startswith("model.") else name          # folders written with that prefix
+        out[key] = t.to(dtype) if t.is_floating_point() else t.clone()
     return out
 
 

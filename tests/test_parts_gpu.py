@@ -348,12 +348,16 @@ def test_toy_arrangement_with_two_mixers_and_no_feed_forward(tmp_path):
         core.end("a"), core.end("b")
         core.cache.check()
         assert core.cache.slots.num_free_slots == 3 and core.cache.groups[0].pool.num_used == 0
-        # the usual arrangement says which of its parts a layer lacks
+        # the usual arrangement says which of its parts a layer lacks: a second norm without a feed-forward (or the
+        # other way round) is refused, a layer with neither is its first half alone
+        norm = PartSpec("rmsnorm", {"size": 48, "eps": 1e-5})
         bad = LayerSpec("pre_norm", PartSpec("toy_decay2", {"hidden_size": 48, "decay": 0.5}), None,
-                        {"norm1": PartSpec("rmsnorm", {"size": 48, "eps": 1e-5})}, {})
+                        {"norm1": norm, "norm2": norm}, {})
         from zedinfer_b200.engine.model import Model
-        with pytest.raises(ValueError, match="ffn.*norm2"):
-            Model(ModelSpec("Toy4ForCausalLM", 300, 48, (bad,), (LayerCall(0),), PartSpec("rmsnorm", {"size": 48, "eps": 1e-5}), True, 128))
+        with pytest.raises(ValueError, match="ffn"):
+            Model(ModelSpec("Toy4ForCausalLM", 300, 48, (bad,), (LayerCall(0),), norm, True, 128))
+        half = LayerSpec("pre_norm", PartSpec("toy_decay2", {"hidden_size": 48, "decay": 0.5}), None, {"norm1": norm}, {})
+        assert Model(ModelSpec("Toy4ForCausalLM", 300, 48, (half,), (LayerCall(0),), norm, True, 128)).blocks[0].ffn is None
     finally:
         unregister_architecture("Toy4ForCausalLM")
         unregister("mixer", "toy_decay2")

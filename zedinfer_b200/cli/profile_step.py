@@ -1,4 +1,5 @@
-"""Run a few decode, prefill or mixed steps of a random-weight Qwen2-shaped model between cudaProfilerStart/Stop,
+"""Run a few decode, prefill or mixed steps of a random-weight model (Qwen2-shaped from the size options, or any
+architecture's config.json given with --config) between cudaProfilerStart/Stop,
 for ``ncu --profile-from-start off``.  Steps are launched kernel by kernel (no CUDA graph), so every
 kernel shows up as a launch of its own.  Prints the mean time of a step measured with CUDA events."""
 from __future__ import annotations
@@ -28,6 +29,7 @@ def main(argv=None) -> int:
     p.add_argument("--intermediate", type=int, default=8960)
     p.add_argument("--vocab", type=int, default=151936)
     p.add_argument("--graphs", action="store_true", help="decode through the captured step instead")
+    p.add_argument("--config", default=None, help="a config.json of any supported architecture instead of the size options")
     p.add_argument("--tcgen05-plain-products", action="store_true",
                    help="plain products of 1,024 rows or more on the tcgen05 kernel instead of the library")
     args = p.parse_args(argv)
@@ -41,6 +43,10 @@ def main(argv=None) -> int:
            "hidden_size": args.hidden, "num_attention_heads": args.heads, "num_key_value_heads": args.kv_heads,
            "head_dim": args.head_dim, "intermediate_size": args.intermediate, "vocab_size": args.vocab,
            "max_position_embeddings": 8192}
+    if args.config:
+        from ..config.registry import load_model_config, read_config_json
+        cfg = read_config_json(args.config)
+        args.vocab = load_model_config(args.config)[2].vocab_size
     span = args.tokens if args.mode == "prefill" else max(args.context + args.steps + 8, args.tokens)
     core = EngineCore(None, "bfloat16", config=cfg, random_seed=3, page_size=16,
                       max_tokens=(args.batch + 1) * (span + 64), max_requests=args.batch + 1, max_seq_len=span + 64,

@@ -28,6 +28,7 @@ class Architecture:
     model_types: Tuple[str, ...]
     parse: Callable[[Mapping[str, Any]], Any]
     build_spec: Callable[[Any], ModelSpec]
+    kernel_libraries: Tuple[str, ...] = ()      # kernel libraries beyond the common ones that its parts call
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -35,8 +36,9 @@ _ARCHITECTURES: Dict[str, Architecture] = {}
 
 def register_architecture(name: str, *, model_types: Tuple[str, ...] = (),
                           parse: Callable[[Mapping[str, Any]], Any],
-                          build_spec: Callable[[Any], ModelSpec]) -> Architecture:
-    arch = Architecture(name, tuple(model_types), parse, build_spec)
+                          build_spec: Callable[[Any], ModelSpec],
+                          kernel_libraries: Tuple[str, ...] = ()) -> Architecture:
+    arch = Architecture(name, tuple(model_types), parse, build_spec, tuple(kernel_libraries))
     _ARCHITECTURES[name] = arch
     return arch
 

@@ -214,7 +214,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
                         const int* __restrict__ tables, const int* __restrict__ tok_seg,
                         const int* __restrict__ pos, int n_heads, int n_kv_heads, int q_blocks, int page_size,
                         int page_shift, int max_blocks, long long page_stride, long long kv_stride, int window,
-                        float scale2) {
+                        float scale2, const float* __restrict__ sinks) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -364,6 +364,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
             acc += po[r] * f;
         }
         const int h = kvh * group + qb * 16 + row;
+        if (sinks) L += exp2f(sinks[h] * LOG2E - M);              // the sink: a term of the denominator without a value
         out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
     }
     cluster.sync();                                               // nobody leaves while its memory is still read
@@ -440,7 +441,8 @@ __device__ __forceinline__ int dt_effective_splits(int tiles, int n_splits, int 
 template <int HD>
 __global__ void __launch_bounds__(HD)
 decode_attention_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out, const int* __restrict__ pos,
-                              int n_heads, int window, int dt_keys, int n_splits, int min_split_tiles) {
+                              int n_heads, int window, int dt_keys, int n_splits, int min_split_tiles,
+                              const float* __restrict__ sinks) {
     const int n = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
     const int P = pos[n];
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
@@ -455,6 +457,7 @@ decode_attention_merge_kernel(const float* __restrict__ part, bf16* __restrict__
         L += src[(size_t)s * (HD + 2) + 1] * f;
         acc += src[(size_t)s * (HD + 2) + 2 + d] * f;
     }
+    if (sinks) L += exp2f(sinks[h] * LOG2E - M);
     out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
 }
 
@@ -464,7 +467,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
                             const int* __restrict__ tables, const int* __restrict__ tok_seg, const int* __restrict__ pos,
                             int* __restrict__ status, int n_heads, int n_kv_heads, int q_blocks, int page_size,
                             int box_rows, int max_blocks, int window, float scale2, int n_splits, int min_split_tiles,
-                            float* __restrict__ part, int kv_box) {
+                            float* __restrict__ part, int kv_box, const float* __restrict__ sinks, int one_plane) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -556,7 +559,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         if (lane < ops) {
             const int key0 = (t_lo + first + tl * CL * 4) * DT_KEYS + pg * box_rows;
             const uint32_t dst = my_ring + st * STAGE_BYTES + hh * (2 * DT_KEYS * 128) + kv * (DT_KEYS * 128) + pg * box_rows * 128;
-            tma_load_5d(dst, &map_kv, hh * 64, key0 % page_size, kvh, kv, page, bar);
+            // a cache with one plane: its rows come in twice, as the keys and as the values
+            tma_load_5d(dst, &map_kv, hh * 64, key0 % page_size, kvh, one_plane ? 0 : kv, page, bar);
         }
         __syncwarp();
     };
@@ -681,6 +685,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         }
         const int h = kvh * group + qb * 16 + row;
         if (eff == 1) {
+            if (sinks) L += exp2f(sinks[h] * LOG2E - M);          // the sink: a term of the denominator without a value
             out[((size_t)n * n_heads + h) * HD + d] = __float2bfloat16_rn(acc / L);
         } else {
             float* dst = part + (((size_t)n * n_heads + h) * n_splits + split) * (HD + 2);
@@ -700,7 +705,8 @@ __global__ void __launch_bounds__(ATT_THREADS)
 prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out,
                          const int* __restrict__ tables, const int* __restrict__ tiles, const int* __restrict__ pos,
                          int n_heads, int n_kv_heads, int page_size, int page_shift, int max_blocks,
-                         long long page_stride, long long kv_stride, int window, float scale2) {
+                         long long page_stride, long long kv_stride, int window, float scale2,
+                         const float* __restrict__ sinks) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int TILE_BYTES = TILE_KEYS * HD * 2;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -783,6 +789,11 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ ca
     l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
     l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
     const int tq = lane & 3;
+    if (sinks) {                                                  // the sink: a term of the denominator without a value
+        const float sk = sinks[h] * LOG2E;
+        l[0] += exp2f(sk - m[0] * scale2);
+        l[1] += exp2f(sk - m[1] * scale2);
+    }
     if (r0 < rows) {
         const float inv = 1.0f / l[0];
         bf16* o = out + ((size_t)(n0 + r0) * n_heads + h) * HD;
@@ -843,7 +854,7 @@ static cudaError_t launch_cluster(K kernel, dim3 grid, dim3 block, size_t smem, 
 ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, const int* tables, const int* tok_seg,
                                   const int* pos, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                   int page_size, int max_blocks, long long page_stride, long long kv_stride,
-                                  int window, float scale, cudaStream_t stream) {
+                                  int window, float scale, const float* sinks, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (check_common("decode_attention", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
     if (n_tokens > 65535) return zi_fail("decode_attention: %d tokens are more than one launch takes (65535)", n_tokens);
@@ -858,13 +869,13 @@ ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, c
         if (set_smem(decode_attention_kernel<128>, smem, "decode_attention")) return 1;
         e = launch_cluster(decode_attention_kernel<128>, grid, dim3(ATT_THREADS), smem, stream,
                            (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tok_seg, pos, n_heads, n_kv_heads,
-                           q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
+                           q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2, sinks);
     } else {
         const size_t smem = 16 * 64 * 2 + DEC_STAGES * 2 * TILE_KEYS * 64 * 2 + (32 + 16 * (64 + 8)) * 4;
         if (set_smem(decode_attention_kernel<64>, smem, "decode_attention")) return 1;
         e = launch_cluster(decode_attention_kernel<64>, grid, dim3(ATT_THREADS), smem, stream,
                            (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tok_seg, pos, n_heads, n_kv_heads,
-                           q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2);
+                           q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2, sinks);
     }
     if (e != cudaSuccess) { cudaGetLastError(); return zi_fail("decode_attention: launch failed: %s", cudaGetErrorString(e)); }
     return zi_check_launch("decode_attention");
@@ -898,7 +909,7 @@ static int dt_max_clusters() {
 struct DtArgs {
     const CUtensorMap* mkv; const void* q; void* out; const int* tables; const int* tok_seg; const int* pos; int* status;
     int n_tokens, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window; float scale2; cudaStream_t stream;
-    int n_splits, min_split_tiles; float* part; int kv_box;
+    int n_splits, min_split_tiles; float* part; int kv_box; const float* sinks; int one_plane;
 };
 
 template <int HD, int KEYS, int CL>
@@ -920,7 +931,7 @@ static cudaError_t dt_launch(const DtArgs& a) {
     cfg.dynamicSmemBytes = dt_smem<HD, KEYS>(); cfg.stream = a.stream;
     return cudaLaunchKernelEx(&cfg, decode_attention_tma_kernel<HD, KEYS, CL>, *a.mkv, (const bf16*)a.q, (bf16*)a.out, a.tables,
                               a.tok_seg, a.pos, a.status, a.n_heads, a.n_kv_heads, a.q_blocks, a.page_size, a.box_rows,
-                              a.max_blocks, a.window, a.scale2, a.n_splits, a.min_split_tiles, a.part, a.kv_box);
+                              a.max_blocks, a.window, a.scale2, a.n_splits, a.min_split_tiles, a.part, a.kv_box, a.sinks, a.one_plane);
 }
 template <int HD>
 static cudaError_t dt_dispatch(const DtArgs& a, int keys, int cl) {
@@ -990,7 +1001,7 @@ ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* ou
                                       const int* pos, int* status, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                       int page_size, int max_blocks, long long n_pages, long long page_stride,
                                       long long kv_stride, int window, float scale, int max_kv_len, float* part,
-                                      long long part_floats, cudaStream_t stream) {
+                                      long long part_floats, const float* sinks, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (check_common("decode_attention_tma", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
     if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1))) return zi_fail("decode_attention_tma: page size %d is not a power of two from 8 to 128", page_size);
@@ -1009,17 +1020,18 @@ ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* ou
     if ((long long)n_kv_heads * q_blocks * plan.splits > 65535) return zi_fail("decode_attention_tma: too many head blocks for one launch");
     const int keys = plan.keys;
     const int box_rows = page_size < keys ? page_size : keys;
-    const int kv_box = box_rows == keys ? 1 : 0;                  // a tile lies in one page: keys and values in one box
+    const int one_plane = kv_stride == 0 ? 1 : 0;                 // one row per token serves as key and as value
+    const int kv_box = (box_rows == keys && !one_plane) ? 1 : 0;  // a tile lies in one page: keys and values in one box
     CUtensorMap mkv;
     if (tc_map_kv_pages(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride, box_rows, kv_box ? 2 : 1)) return 1;
     DtArgs a = {&mkv, q, out, tables, tok_seg, pos, status, n_tokens, n_heads, n_kv_heads, q_blocks, page_size, box_rows,
-                max_blocks, window, scale * LOG2E, stream, plan.splits, plan.min_split_tiles, part, kv_box};
+                max_blocks, window, scale * LOG2E, stream, plan.splits, plan.min_split_tiles, part, kv_box, sinks, one_plane};
     cudaError_t e = head_dim == 128 ? dt_dispatch<128>(a, keys, plan.cl) : dt_dispatch<64>(a, keys, plan.cl);
     if (e != cudaSuccess) { cudaGetLastError(); return zi_fail("decode_attention_tma: launch failed: %s", cudaGetErrorString(e)); }
     if (plan.splits > 1) {
         const dim3 grid(n_tokens, n_heads);
-        if (head_dim == 128) decode_attention_merge_kernel<128><<<grid, 128, 0, stream>>>(part, (bf16*)out, pos, n_heads, window, keys, plan.splits, plan.min_split_tiles);
-        else decode_attention_merge_kernel<64><<<grid, 64, 0, stream>>>(part, (bf16*)out, pos, n_heads, window, keys, plan.splits, plan.min_split_tiles);
+        if (head_dim == 128) decode_attention_merge_kernel<128><<<grid, 128, 0, stream>>>(part, (bf16*)out, pos, n_heads, window, keys, plan.splits, plan.min_split_tiles, sinks);
+        else decode_attention_merge_kernel<64><<<grid, 64, 0, stream>>>(part, (bf16*)out, pos, n_heads, window, keys, plan.splits, plan.min_split_tiles, sinks);
     }
     return zi_check_launch("decode_attention_tma");
 }
@@ -1027,7 +1039,7 @@ ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* ou
 ZI_EXPORT int zi_prefill_attention(const void* q, const void* cache, void* out, const int* tables, const int* tiles,
                                    const int* pos, int n_tiles, int n_heads, int n_kv_heads, int head_dim,
                                    int page_size, int max_blocks, long long page_stride, long long kv_stride,
-                                   int window, float scale, cudaStream_t stream) {
+                                   int window, float scale, const float* sinks, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (check_common("prefill_attention", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
     if (n_heads > 65535) return zi_fail("prefill_attention: %d heads are more than one launch takes", n_heads);
@@ -1039,13 +1051,13 @@ ZI_EXPORT int zi_prefill_attention(const void* q, const void* cache, void* out, 
         if (set_smem(prefill_attention_kernel<128>, smem, "prefill_attention")) return 1;
         prefill_attention_kernel<128><<<grid, ATT_THREADS, smem, stream>>>(
             (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tiles, pos, n_heads, n_kv_heads, page_size, shift,
-            max_blocks, page_stride, kv_stride, window, scale2);
+            max_blocks, page_stride, kv_stride, window, scale2, sinks);
     } else {
         const size_t smem = 5 * TILE_KEYS * 64 * 2;
         if (set_smem(prefill_attention_kernel<64>, smem, "prefill_attention")) return 1;
         prefill_attention_kernel<64><<<grid, ATT_THREADS, smem, stream>>>(
             (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tiles, pos, n_heads, n_kv_heads, page_size, shift,
-            max_blocks, page_stride, kv_stride, window, scale2);
+            max_blocks, page_stride, kv_stride, window, scale2, sinks);
     }
     return zi_check_launch("prefill_attention");
 }

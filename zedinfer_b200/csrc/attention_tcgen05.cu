@@ -105,6 +105,8 @@ struct FaParams {
     int* status;
     int n_heads, n_kv_heads, page_size, max_blocks, window;
     float scale2;                  // softmax scale x log2(e)
+    const float* sinks;            // optional, one float per query head: exp(sinks[h]) joins the softmax's denominator
+    int one_plane;                 // the cache has one plane, whose rows are keys and values at once
 };
 
 // TMEM columns of a CTA: two score buffers, the output, and the two A operands (bfloat16 pairs, one row per lane)
@@ -192,7 +194,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, con
             __syncwarp();
             if (my_op) {
                 const uint32_t dst = tc_smem_u32(kv ? sV : sK) + st * TILE_BYTES + my_hh * SUB + my_pg * p.page_size * 128;
-                tma_load_5d(dst, &map_kv, my_hh * 64, 0, kvh, kv, page, bar);
+                tma_load_5d(dst, &map_kv, my_hh * 64, 0, kvh, p.one_plane ? 0 : kv, page, bar);
             }
             __syncwarp();
         };
@@ -396,6 +398,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, con
             if (lane == 0) { atomicExch(p.status, 14); gave_up = 1; }
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (p.sinks && m_used != -INFINITY) l += exp2f(p.sinks[h] * 1.4426950408889634f - m_used);   // no key, no value
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             // the whole row of O with one wait (the registers of the scores are free now)
 #pragma unroll
@@ -433,7 +436,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, con
 ZI_EXPORT int zi_prefill_attention_tcgen05(const void* q, const void* cache, void* out, const int* tables, const int* tiles,
                                            const int* pos, int* status, int n_tokens, int n_tiles, int n_heads, int n_kv_heads,
                                            int head_dim, int page_size, int max_blocks, long long n_pages, long long page_stride,
-                                           long long kv_stride, int window, float scale, cudaStream_t stream) {
+                                           long long kv_stride, int window, float scale, const float* sinks,
+                                           cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return 0;
     if (head_dim != 64 && head_dim != 128) return zi_fail("prefill_attention_tcgen05: head_dim %d is not 64 or 128", head_dim);
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return zi_fail("prefill_attention_tcgen05: %d heads over %d key-value heads", n_heads, n_kv_heads);
@@ -449,6 +453,7 @@ ZI_EXPORT int zi_prefill_attention_tcgen05(const void* q, const void* cache, voi
     p.q = (const bf16*)q; p.out = (bf16*)out; p.tables = tables; p.tiles = tiles; p.pos = pos; p.status = status;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.max_blocks = max_blocks; p.window = window;
     p.scale2 = scale * 1.4426950408889634f;
+    p.sinks = sinks; p.one_plane = kv_stride == 0 ? 1 : 0;
     const dim3 grid(n_heads, n_tiles);
     const size_t smem = (size_t)FA_STAGE_OFFSET(head_dim) + (size_t)FA_ROWS * head_dim * 2;
     cudaError_t e;

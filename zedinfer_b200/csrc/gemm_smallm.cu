@@ -140,11 +140,16 @@ __device__ __forceinline__ void accumulate_rows(float (&acc)[NT][4], const bf16*
 // Slot (tq*2, tq*2+1) of A meets slot (tq*2, tq*2+1) of B and slot (tq*2+8, +9) meets (tq*2+8, +9): each
 // pairs weight and activation of the same k.
 
+// What the epilogue does to the sums.  kind 0: the template's own rule (SILU_MUL: up * silu(gate); else + bias);
+// kind 2 (with SILU_MUL, W = [gate; up]): g = min(gate, limit), u = clamp(up, -limit, limit) (limit <= 0: no clamps),
+// g * sigmoid(slope * g) * (u + up_offset); kind 3 (without): max(x, 0)^2.
+struct GsAct { int kind; float limit, slope, up_offset; };
+
 template <int NT, typename TC, bool SILU_MUL>
 __global__ void __launch_bounds__(GS_THREADS, NT == 1 ? 4 : 3)
 gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const bf16* __restrict__ bias,
                    TC* __restrict__ C, float* __restrict__ part, int* __restrict__ counters, int M, int N, int K,
-                   long long ldx, long long ldw, long long ldc, int cluster_reduce) {
+                   long long ldx, long long ldw, long long ldc, int cluster_reduce, GsAct act) {
     // N: number of output columns.  With SILU_MUL, W has 2*N rows (gate rows, then up rows).
     // gridDim.y > 1: K is cut into gridDim.y ranges, one block each; the blocks of a column tile leave their
     // sums in `part` [gridDim.y][16][N] and the last one to arrive adds them in range order.
@@ -240,9 +245,19 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
             for (int w = 0; w < GS_WARPS; ++w) u += red[SILU_MUL ? 1 : 0][w][r][m];
             // the unfused path rounds gate and up to bfloat16 before the activation; do the same
             const float gr = __bfloat162float(__float2bfloat16_rn(v)), ur = __bfloat162float(__float2bfloat16_rn(u));
-            v = ur * gr / (1.0f + expf(-gr));
+            if (act.kind == 2) {
+                float g2 = gr, u2 = ur;
+                if (act.limit > 0.0f) { g2 = fminf(g2, act.limit); u2 = fminf(fmaxf(u2, -act.limit), act.limit); }
+                v = (g2 / (1.0f + expf(-act.slope * g2))) * (u2 + act.up_offset);
+            } else {
+                v = ur * gr / (1.0f + expf(-gr));
+            }
         } else if (bias) {
             v += __bfloat162float(bias[n]);
+        } else if (act.kind == 3) {
+            // the unfused path rounds the product to the output's type before the activation; do the same
+            const float x = fmaxf(to_f32<TC>(from_f32<TC>(v)), 0.0f);
+            v = x * x;
         }
         C[(long long)m * ldc + n] = from_f32<TC>(v);
     }
@@ -252,7 +267,7 @@ gemm_smallm_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const
 template <int NT, typename TC, bool SILU>
 static void launch(const void* X, const void* W, const void* bias, void* C, float* part, int* counters, int ksplit,
                    int M, int N, int K, long long ldx, long long ldw, long long ldc, cudaStream_t stream,
-                   bool through_clusters = true) {
+                   bool through_clusters = true, GsAct act = GsAct{0, 0.0f, 0.0f, 0.0f}) {
     if (through_clusters && ksplit > 1 && ksplit <= 8) {
         // the K ranges of a column tile as one cluster along y: their sums meet in distributed shared memory
         cudaLaunchConfig_t cfg;
@@ -265,11 +280,11 @@ static void launch(const void* X, const void* W, const void* bias, void* C, floa
         attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = ksplit; attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr; cfg.numAttrs = 1;
         if (cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<NT, TC, SILU>, (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C,
-                               part, counters, M, N, K, ldx, ldw, ldc, 1) == cudaSuccess) return;
+                               part, counters, M, N, K, ldx, ldw, ldc, 1, act) == cudaSuccess) return;
         cudaGetLastError();                             // no cluster of that shape here: the way through global memory
     }
     zi_launch(gemm_smallm_kernel<NT, TC, SILU>, dim3((N + 15) / 16, ksplit), dim3(GS_THREADS), 0, stream,
-              (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C, part, counters, M, N, K, ldx, ldw, ldc, 0);
+              (const bf16*)X, (const bf16*)W, (const bf16*)bias, (TC*)C, part, counters, M, N, K, ldx, ldw, ldc, 0, act);
 }
 
 // How many ranges K is cut into: a function of the weight's shape only.  Few column tiles (narrow outputs)
@@ -298,9 +313,14 @@ ZI_EXPORT int zi_gemm_smallm_max_rows() { return 16; }
 // silu_mul != 0: W is [2*N, K] (gate rows then up rows), C[m, n] = up * silu(gate); bias must be null.
 ZI_EXPORT int zi_gemm_smallm(const void* X, const void* W, const void* bias, void* C, int c_dtype, float* part,
                              int* counters, int M, int N, int K, long long ldx, long long ldw, long long ldc,
-                             int silu_mul, cudaStream_t stream) {
+                             int silu_mul, int act_kind, float act_limit, float act_slope, float act_offset,
+                             cudaStream_t stream) {
+    // act_kind: see GsAct (2 needs silu_mul's stacked weight, 3 a plain product without bias)
     if (M <= 0 || N <= 0) return 0;
     if (M > 16) return zi_fail("gemm_smallm: M=%d rows; this kernel takes at most 16", M);
+    if ((act_kind == 2 && !silu_mul) || (act_kind == 3 && (silu_mul || bias)) || (act_kind != 0 && act_kind != 2 && act_kind != 3))
+        return zi_fail("gemm_smallm: activation %d does not fit this product", act_kind);
+    const GsAct act = {act_kind, act_limit, act_slope, act_offset};
     if (K <= 0 || K % 32 != 0) return zi_fail("gemm_smallm: K=%d must be a positive multiple of 32", K);
     if (ldx % 8 != 0 || ldw % 8 != 0) return zi_fail("gemm_smallm: row strides (%lld, %lld) must be multiples of 8 elements", ldx, ldw);
     if (((uintptr_t)X | (uintptr_t)W) & 15) return zi_fail("gemm_smallm: operands must be 16-byte aligned");
@@ -310,11 +330,11 @@ ZI_EXPORT int zi_gemm_smallm(const void* X, const void* W, const void* bias, voi
     const int ksplit = zi_gemm_smallm_ksplit(N, K, silu_mul);
     if (ksplit > 1 && (!part || !counters)) return zi_fail("gemm_smallm: N=%d K=%d is split %d ways and needs scratch", N, K, ksplit);
     if (silu_mul) {
-        if (M <= 8) { if (f32) launch<1, float, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<1, bf16, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
-        else        { if (f32) launch<2, float, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
+        if (M <= 8) { if (f32) launch<1, float, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, true, act); else launch<1, bf16, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, true, act); }
+        else        { if (f32) launch<2, float, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, true, act); else launch<2, bf16, true>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, true, act); }
     } else {
-        if (M <= 8) { if (f32) launch<1, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<1, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
-        else        { if (f32) launch<2, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); else launch<2, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream); }
+        if (M <= 8) { if (f32) launch<1, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, true, act); else launch<1, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, true, act); }
+        else        { if (f32) launch<2, float, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, true, act); else launch<2, bf16, false>(X, W, bias, C, part, counters, ksplit, M, N, K, ldx, ldw, ldc, stream, true, act); }
     }
     return zi_check_launch("gemm_smallm");
 }

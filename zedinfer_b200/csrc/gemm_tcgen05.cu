@@ -178,6 +178,8 @@ struct TpParams {
     long long ldc;
     int M, N, K;                // N: columns of C (silu_mul: the intermediate size)
     int c_is_f32, silu_mul;
+    int act;                    // 1: up * silu(gate); 2: the clamped, sigmoid-gated product (both with silu_mul's stacked
+    float act_limit, act_slope, act_offset;   // weight); 3: max(x, 0)^2 on a plain product; 0: nothing
     int bn;                     // accumulator columns per tile
     int up_row0;                // silu_mul: first row of the up half in W
     int tiles_m, tiles_n;
@@ -222,8 +224,16 @@ __device__ __forceinline__ void tp_epilogue_row(const TpParams& p, uint32_t tadd
                     float v[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const float gv = __uint_as_float(g[q][16 * h + j]);
-                        v[j] = __fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[q][16 * h + j]);
+                        float gv = __uint_as_float(g[q][16 * h + j]), uv = __uint_as_float(u[q][16 * h + j]);
+                        if (p.act == 2) {
+                            // both halves rounded to bfloat16 first, as a separate product would have stored them
+                            gv = __bfloat162float(__float2bfloat16_rn(gv));
+                            uv = __bfloat162float(__float2bfloat16_rn(uv));
+                            if (p.act_limit > 0.0f) { gv = fminf(gv, p.act_limit); uv = fminf(fmaxf(uv, -p.act_limit), p.act_limit); }
+                            v[j] = __fdividef(gv, 1.0f + __expf(-p.act_slope * gv)) * (uv + p.act_offset);
+                        } else {
+                            v[j] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                        }
                     }
                     tp_store16(p, (long long)m * p.ldc + n0 + c, n0 + c, v);
                 }
@@ -249,6 +259,13 @@ __device__ __forceinline__ void tp_epilogue_row(const TpParams& p, uint32_t tadd
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         v[j] = __uint_as_float(r[q][16 * h + j]) + ((p.bias && n0 + c + j < p.N) ? __bfloat162float(p.bias[n0 + c + j]) : 0.0f);
+                    if (p.act == 3) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float x = fmaxf(__bfloat162float(__float2bfloat16_rn(v[j])), 0.0f);
+                            v[j] = x * x;
+                        }
+                    }
                     tp_store16(p, (long long)m * p.ldc + n0 + c, n0 + c, v);
                 }
             }
@@ -568,27 +585,30 @@ static int tp_step_cost(int bn) { const int pipe = bn / 2, smem = 32 + bn / 4; r
 
 // C[M,N] = X[M,K] . W^T with the persistent kernel.  epilogue 0: W is [N,K], optional bias[N].
 // epilogue 1 (silu_mul): W is [2N,K] = [gate; up], C = silu(X.gate^T) * (X.up^T), no bias.
+// epilogue 2: the same stacked weight, C = g * sigmoid(slope * g) * (u + offset) with g = min(gate, limit), u = clamp(up,
+// -limit, limit) (limit <= 0: no clamps); epilogue 3: W is [N,K], C = max(X.W^T, 0)^2, no bias.
 // bn_hint: 0 lets the call choose the tile width; else a multiple of 16 (32 for silu_mul) up to 256.
 ZI_EXPORT int zi_gemm_tcgen05_tiles(const void* X, const void* W, const void* bias, void* C, int c_dtype, int* status, int M, int N,
                                     int K, long long ldx, long long ldw, long long ldc, int epilogue, int bn_hint, int num_sms,
-                                    cudaStream_t stream) {
+                                    float act_limit, float act_slope, float act_offset, cudaStream_t stream) {
+    const bool gated = epilogue == 1 || epilogue == 2;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return zi_fail("gemm_tcgen05: K=%d must be positive", K);
     if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return zi_fail("gemm_tcgen05: K and the row strides must be multiples of 8 elements (16 bytes) for TMA; got K=%d ldx=%lld ldw=%lld", K, ldx, ldw);
     if (((uintptr_t)X | (uintptr_t)W) & 15) return zi_fail("gemm_tcgen05: operands must be 16-byte aligned");
     if (c_dtype != ZI_F32 && c_dtype != ZI_BF16) return zi_fail("gemm_tcgen05: unknown output dtype %d", c_dtype);
-    if (epilogue != 0 && epilogue != 1) return zi_fail("gemm_tcgen05: unknown epilogue %d", epilogue);
-    if (epilogue == 1 && bias) return zi_fail("gemm_tcgen05: the silu_mul epilogue takes no bias");
+    if (epilogue < 0 || epilogue > 3) return zi_fail("gemm_tcgen05: unknown epilogue %d", epilogue);
+    if (epilogue != 0 && bias) return zi_fail("gemm_tcgen05: the silu_mul epilogue takes no bias");
     if (!status) return zi_fail("gemm_tcgen05: a status word is required");
     if (num_sms <= 0) return zi_fail("gemm_tcgen05: num_sms=%d must be positive", num_sms);
     if (tc_init()) return 1;
-    const int step = epilogue == 1 ? 32 : 16;              // silu_mul: both halves are multiples of 16 columns
+    const int step = gated ? 32 : 16;              // silu_mul: both halves are multiples of 16 columns
     const int tiles_m = (M + TC_BM - 1) / TC_BM;
     int bn = bn_hint;
     if (bn == 0) {
         long long best = -1;
         for (int cand = 256; cand >= step; cand -= step) {
-            const int cols = epilogue == 1 ? cand / 2 : cand;
+            const int cols = gated ? cand / 2 : cand;
             const long long tiles = (long long)tiles_m * ((N + cols - 1) / cols);
             const long long cost = ((tiles + num_sms - 1) / num_sms) * tp_step_cost(cand);
             if (best < 0 || cost < best) { best = cost; bn = cand; }
@@ -597,15 +617,15 @@ ZI_EXPORT int zi_gemm_tcgen05_tiles(const void* X, const void* W, const void* bi
     if (bn < step || bn > 256 || bn % step) return zi_fail("gemm_tcgen05: tile width %d must be a multiple of %d up to 256", bn, step);
     TpParams p;
     p.C = C; p.bias = (const bf16*)bias; p.status = status; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
-    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = epilogue; p.bn = bn; p.up_row0 = N;
+    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = gated ? 1 : 0; p.act = epilogue; p.act_limit = act_limit; p.act_slope = act_slope; p.act_offset = act_offset; p.bn = bn; p.up_row0 = N;
     p.tiles_m = tiles_m;
-    const int cols = epilogue == 1 ? bn / 2 : bn;
+    const int cols = gated ? bn / 2 : bn;
     p.tiles_n = (N + cols - 1) / cols;
     const long long n_tiles = (long long)p.tiles_m * p.tiles_n;
     if (n_tiles > 0x7fffffffLL) return zi_fail("gemm_tcgen05: too many tiles");
     CUtensorMap ma, mb;
     if (tc_make_map(&ma, X, M, K, ldx, TC_BM)) return 1;
-    if (tc_make_map(&mb, W, epilogue == 1 ? 2LL * N : N, K, ldw, bn / 2)) return 1;
+    if (tc_make_map(&mb, W, gated ? 2LL * N : N, K, ldw, bn / 2)) return 1;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TP_SMEM);
@@ -622,14 +642,16 @@ static int tq_step_cost(int bn) { const int pipe = bn / 2, smem = 32 + bn / 8; r
 // The same product on pairs of SMs (256-row tiles).  Arguments as zi_gemm_tcgen05_tiles, without num_sms:
 // the number of pairs that fit on the device at once is asked of the runtime.
 ZI_EXPORT int zi_gemm_tcgen05_pairs(const void* X, const void* W, const void* bias, void* C, int c_dtype, int* status, int M, int N,
-                                    int K, long long ldx, long long ldw, long long ldc, int epilogue, int bn_hint, cudaStream_t stream) {
+                                    int K, long long ldx, long long ldw, long long ldc, int epilogue, int bn_hint,
+                                    float act_limit, float act_slope, float act_offset, cudaStream_t stream) {
+    const bool gated = epilogue == 1 || epilogue == 2;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return zi_fail("gemm_tcgen05: K=%d must be positive", K);
     if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return zi_fail("gemm_tcgen05: K and the row strides must be multiples of 8 elements (16 bytes) for TMA; got K=%d ldx=%lld ldw=%lld", K, ldx, ldw);
     if (((uintptr_t)X | (uintptr_t)W) & 15) return zi_fail("gemm_tcgen05: operands must be 16-byte aligned");
     if (c_dtype != ZI_F32 && c_dtype != ZI_BF16) return zi_fail("gemm_tcgen05: unknown output dtype %d", c_dtype);
-    if (epilogue != 0 && epilogue != 1) return zi_fail("gemm_tcgen05: unknown epilogue %d", epilogue);
-    if (epilogue == 1 && bias) return zi_fail("gemm_tcgen05: the silu_mul epilogue takes no bias");
+    if (epilogue < 0 || epilogue > 3) return zi_fail("gemm_tcgen05: unknown epilogue %d", epilogue);
+    if (epilogue != 0 && bias) return zi_fail("gemm_tcgen05: the silu_mul epilogue takes no bias");
     if (!status) return zi_fail("gemm_tcgen05: a status word is required");
     if (tc_init()) return 1;
     cudaLaunchConfig_t cfg = {};
@@ -650,13 +672,13 @@ ZI_EXPORT int zi_gemm_tcgen05_pairs(const void* X, const void* W, const void* bi
         if (e != cudaSuccess || n <= 0) return zi_fail("gemm_tcgen05: no pair of CTAs of this kernel fits on the device (%s)", cudaGetErrorString(e));
         max_pairs = n;
     }
-    const int step = epilogue == 1 ? 32 : 16;
+    const int step = gated ? 32 : 16;
     const int tiles_m = (M + 255) / 256;
     int bn = bn_hint;
     if (bn == 0) {
         long long best = -1;
         for (int cand = 256; cand >= step; cand -= step) {
-            const int cols = epilogue == 1 ? cand / 2 : cand;
+            const int cols = gated ? cand / 2 : cand;
             const long long tiles = (long long)tiles_m * ((N + cols - 1) / cols);
             const long long cost = ((tiles + max_pairs - 1) / max_pairs) * tq_step_cost(cand);
             if (best < 0 || cost < best) { best = cost; bn = cand; }
@@ -665,15 +687,15 @@ ZI_EXPORT int zi_gemm_tcgen05_pairs(const void* X, const void* W, const void* bi
     if (bn < step || bn > 256 || bn % step) return zi_fail("gemm_tcgen05: tile width %d must be a multiple of %d up to 256", bn, step);
     TpParams p;
     p.C = C; p.bias = (const bf16*)bias; p.status = status; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
-    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = epilogue; p.bn = bn; p.up_row0 = N;
+    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = gated ? 1 : 0; p.act = epilogue; p.act_limit = act_limit; p.act_slope = act_slope; p.act_offset = act_offset; p.bn = bn; p.up_row0 = N;
     p.tiles_m = tiles_m;
-    const int cols = epilogue == 1 ? bn / 2 : bn;
+    const int cols = gated ? bn / 2 : bn;
     p.tiles_n = (N + cols - 1) / cols;
     const long long n_tiles = (long long)p.tiles_m * p.tiles_n;
     if (n_tiles > 0x7fffffffLL) return zi_fail("gemm_tcgen05: too many tiles");
     CUtensorMap ma, mb;
     if (tc_make_map(&ma, X, M, K, ldx, TC_BM)) return 1;
-    if (tc_make_map(&mb, W, epilogue == 1 ? 2LL * N : N, K, ldw, bn / 2)) return 1;
+    if (tc_make_map(&mb, W, gated ? 2LL * N : N, K, ldw, bn / 2)) return 1;
     cfg.gridDim = dim3(2 * (unsigned)(n_tiles < max_pairs ? n_tiles : max_pairs));
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel, ma, mb, p);
     if (e != cudaSuccess) return zi_fail("gemm_tcgen05_pairs: launch failed: %s", cudaGetErrorString(e));

@@ -166,8 +166,12 @@ static inline int tc_map_kv_pages(CUtensorMap* out, const void* cache, int head_
     auto it = tc_kv_maps.find(key);
     if (it == tc_kv_maps.end()) {
         if (tc_kv_maps.size() > 4096) tc_kv_maps.clear();
-        cuuint64_t dims[5] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)n_kv_heads, 2, (cuuint64_t)n_pages};
-        cuuint64_t strides[4] = {(cuuint64_t)head_dim * 2, (cuuint64_t)page_size * head_dim * 2, (cuuint64_t)kv_stride * 2, (cuuint64_t)page_stride * 2};
+        // kv_stride 0: a cache with one plane (rows that are keys and values at once); the plane axis then has one
+        // entry, and a stride that is never used (a tensor map takes no stride of zero)
+        const bool one_plane = kv_stride == 0;
+        cuuint64_t dims[5] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)n_kv_heads, (cuuint64_t)(one_plane ? 1 : 2), (cuuint64_t)n_pages};
+        cuuint64_t strides[4] = {(cuuint64_t)head_dim * 2, (cuuint64_t)page_size * head_dim * 2,
+                                 (cuuint64_t)(one_plane ? page_stride : kv_stride) * 2, (cuuint64_t)page_stride * 2};
         cuuint32_t box[5] = {64, (cuuint32_t)box_rows, 1, (cuuint32_t)(box_kv == 2 ? 2 : 1), 1};
         cuuint32_t estr[5] = {1, 1, 1, 1, 1};
         CUtensorMap m;

@@ -233,11 +233,18 @@ class EngineCore:
         self.capture_safe = not self.capture_blockers
 
     @staticmethod
-    def kernel_libraries(dtype) -> List[str]:
-        """The kernel libraries a run in ``dtype`` loads, for building them ahead of the first step."""
+    def kernel_libraries(dtype, model_dir: Optional[str] = None) -> List[str]:
+        """The kernel libraries a run in ``dtype`` loads, for building them ahead of the first step (side by side, not
+        one after the other as first uses would).  ``model_dir``: also what that model's architecture names."""
         libs = ["elementwise", "gemm_simt", "attention_generic", "sampling"]
         if parse_dtype(dtype) == torch.bfloat16:
             libs += ["attention_mma", "gemm_smallm"]      # the tcgen05 libraries are built when a step first needs them
+        if model_dir is not None:
+            from ..config.registry import read_config_json, resolve_architecture
+            extra = resolve_architecture(read_config_json(model_dir)).kernel_libraries
+            libs += [name for name in extra if name not in libs]
+            if extra and parse_dtype(dtype) == torch.bfloat16:
+                libs += ["attention_tcgen05", "gemm_tcgen05"]
         return libs
 
     # ---- requests -------------------------------------------------------------------------

@@ -48,7 +48,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     from .core import EngineCore, StepEntry
 
     print("[trace_run] preparing kernels (compiled at the first call) ...", file=sys.stderr, flush=True)
-    build.compile_all(EngineCore.kernel_libraries(args.dtype))
+    build.compile_all(EngineCore.kernel_libraries(args.dtype, args.model), jobs=8)
     print(f"[trace_run] loading {args.model} as {args.dtype} ...", file=sys.stderr, flush=True)
     core = EngineCore(args.model, args.dtype, page_size=PAGE_SIZE, max_tokens=args.max_tokens,
                       max_requests=MAX_LIVE, max_seq_len=args.max_tokens)

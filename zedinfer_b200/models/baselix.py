@@ -216,4 +216,5 @@ def build_baselix_spec(cfg: BaselixConfig) -> ModelSpec:
                                       "softcap": cfg.logit_softcap}))
 
 
-BASELIX = register_architecture("Baselix", model_types=("baselix",), parse=parse_baselix_config, build_spec=build_baselix_spec)
+BASELIX = register_architecture("Baselix", model_types=("baselix",), parse=parse_baselix_config, build_spec=build_baselix_spec,
+                                kernel_libraries=("rowwise", "moe"))

@@ -33,7 +33,7 @@ SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "rope_table", "gemm_smallm_rope", "can_fuse_rope_product", "silu_mul", "add", "cast",
            "gemm_nt", "linear", "linear_for_residual", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode",
            "embedding_positions", "softcap", "relu2", "gated_clamp_mul", "rmsnorm_append", "linear_per_head", "route_topk",
-           "moe_group", "moe_gemm", "moe_combine"]
+           "moe_group", "moe_gemm", "moe_combine", "linear_gated_clamp_mul", "linear_relu2"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -251,10 +251,14 @@ def _small_m_ok(x: torch.Tensor, w: torch.Tensor, fused: Optional[str] = None) -
 
 
 def gemm_smallm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                silu_mul: bool = False) -> None:
+                silu_mul: bool = False, gated: Optional[tuple] = None, relu2: bool = False) -> None:
     """``out = x @ w.T + bias`` for at most 16 rows of ``x``: weights stream once from memory into the
     tensor cores.  ``silu_mul``: ``w`` is ``[2*I, K]`` (gate rows, then up rows) and ``out[m, j] =
-    up * gate / (1 + exp(-gate))``."""
+    up * gate / (1 + exp(-gate))``.  ``gated = (limit, slope, up_offset)``: the same stacked weight with the clamped,
+    sigmoid-gated product of :func:`gated_clamp_mul` in the epilogue.  ``relu2``: ``out = max(x @ w.T, 0)^2``."""
+    silu_mul = silu_mul or gated is not None
+    kind = 2 if gated is not None else (3 if relu2 else 0)
+    limit, slope, up_offset = gated if gated is not None else (0.0, 0.0, 0.0)
     need_cuda(x, w, bias, out)
     m, k = x.shape
     n = w.shape[0] // 2 if silu_mul else w.shape[0]
@@ -265,7 +269,8 @@ def gemm_smallm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
     part, counters = _smallm_scratch(x.device, n, k, silu_mul)
     _gemm_smallm.call("zi_gemm_smallm", ptr(x), ptr(w), ptr(bias), ptr(out), c_int(dtype_code(out.dtype)), ptr(part),
                       ptr(counters), c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)),
-                      c_ll(out.stride(0)), c_int(1 if silu_mul else 0), stream())
+                      c_ll(out.stride(0)), c_int(1 if silu_mul else 0), c_int(kind), c_float(limit), c_float(slope),
+                      c_float(up_offset), stream())
 
 
 _scratch = {}
@@ -346,16 +351,22 @@ def _num_sms(device) -> int:
 
 
 def gemm_tcgen05_tiles(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                       silu_mul: bool = False, tile_width: int = 0, pairs: Optional[bool] = None) -> None:
+                       silu_mul: bool = False, tile_width: int = 0, pairs: Optional[bool] = None,
+                       gated: Optional[tuple] = None, relu2: bool = False) -> None:
     """``out = x @ w.T + bias`` for many rows: one persistent CTA per SM walks 128-row tiles, the accumulator
     double-buffered in TMEM so that the epilogue of a tile overlaps the products of the next.
 
     With ``silu_mul`` the weight is ``[gate; up]`` stacked (``[2 * n, k]``) and ``out[m, n] = silu(x.gate^T) *
     (x.up^T)``; neither half is written to memory.  ``tile_width`` (accumulator columns per tile) is chosen by
     the call when 0.  ``pairs``: two SMs share a 256-row tile and each loads only half of its weight rows
-    (``cta_group::2``); the default for more than 128 rows.
+    (``cta_group::2``); the default for more than 128 rows.  ``gated = (limit, slope, up_offset)``: the stacked weight
+    with the clamped, sigmoid-gated product of :func:`gated_clamp_mul` in the epilogue; ``relu2``: ``out = max(x @ w.T,
+    0)^2``.
     """
     need_cuda(x, w, bias, out)
+    silu_mul = silu_mul or gated is not None
+    epilogue = 2 if gated is not None else (3 if relu2 else (1 if silu_mul else 0))
+    limit, slope, up_offset = gated if gated is not None else (0.0, 0.0, 0.0)
     m, k = x.shape
     n = out.shape[1]
     if w.shape != ((2 * n if silu_mul else n), k) or out.shape[0] != m or out.stride(1) != 1 or x.stride(1) != 1 or w.stride(1) != 1:
@@ -367,11 +378,13 @@ def gemm_tcgen05_tiles(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Te
     if pairs:
         _gemm_tcgen05.call("zi_gemm_tcgen05_pairs", ptr(x), ptr(w), ptr(bias), ptr(out), c_int(dtype_code(out.dtype)),
                            ptr(_tc_status(x.device)), c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)),
-                           c_ll(out.stride(0)), c_int(1 if silu_mul else 0), c_int(tile_width), stream())
+                           c_ll(out.stride(0)), c_int(epilogue), c_int(tile_width), c_float(limit), c_float(slope),
+                           c_float(up_offset), stream())
         return
     _gemm_tcgen05.call("zi_gemm_tcgen05_tiles", ptr(x), ptr(w), ptr(bias), ptr(out), c_int(dtype_code(out.dtype)),
                        ptr(_tc_status(x.device)), c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(w.stride(0)),
-                       c_ll(out.stride(0)), c_int(1 if silu_mul else 0), c_int(tile_width), c_int(_num_sms(x.device)), stream())
+                       c_ll(out.stride(0)), c_int(epilogue), c_int(tile_width), c_int(_num_sms(x.device)), c_float(limit),
+                       c_float(slope), c_float(up_offset), stream())
 
 
 def status_word(device) -> torch.Tensor:
@@ -434,6 +447,42 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[tor
     gate_up = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=out.dtype, device=x.device)
     linear(x, w_gate_up, bias, gate_up)
     silu_mul(gate_up, out)
+
+
+def linear_gated_clamp_mul(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float,
+                           up_offset: float) -> None:
+    """``out = g * sigmoid(slope * g) * (u + up_offset)`` with ``g = min(x @ gate.T, limit)``, ``u = clamp(x @ up.T,
+    -limit, limit)`` and ``w_gate_up = [gate; up]`` stacked (``limit <= 0``: no clamps).  Where :func:`linear_silu_mul`
+    runs its activation in the product's epilogue this one does too, by the same rules; otherwise product, then
+    :func:`gated_clamp_mul`."""
+    need_cuda(x, w_gate_up, out)
+    gated = (float(limit), float(slope), float(up_offset))
+    if _small_m_ok(x, w_gate_up, fused="silu"):
+        gemm_smallm(x, w_gate_up, None, out, gated=gated)
+        return
+    min_rows = TC_FUSED_MIN_ROWS_LARGE if w_gate_up.shape[0] * w_gate_up.shape[1] >= TC_FUSED_LARGE_ELEMENTS else TC_FUSED_MIN_ROWS
+    if x.shape[0] >= min_rows and out.dtype == torch.bfloat16 and _tc_ok(x, w_gate_up, None, out):
+        gemm_tcgen05_tiles(x, w_gate_up, None, out, gated=gated)
+        _tc_launched[x.device] = True
+        return
+    gate_up = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=out.dtype, device=x.device)
+    linear(x, w_gate_up, None, gate_up)
+    gated_clamp_mul(gate_up, out, *gated)
+
+
+def linear_relu2(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = max(x @ w.T, 0)^2``: the activation in the product's epilogue on the weight-streaming kernel (up to 16
+    rows) and on the tcgen05 kernel (from ``TC_FUSED_MIN_ROWS`` rows); otherwise product, then :func:`relu2`."""
+    need_cuda(x, w, out)
+    if _small_m_ok(x, w) and out.stride(1) == 1:
+        gemm_smallm(x, w, None, out, relu2=True)
+        return
+    if x.shape[0] >= TC_FUSED_MIN_ROWS and out.dtype == torch.bfloat16 and _tc_ok(x, w, None, out):
+        gemm_tcgen05_tiles(x, w, None, out, relu2=True)
+        _tc_launched[x.device] = True
+        return
+    linear(x, w, None, out)
+    relu2(out, out)
 
 
 # A product whose result goes straight into the residual stream (output and down projections), with 17 to 256 rows:
@@ -535,12 +584,20 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tab
 PREFILL_TILE_ROWS = 128          # query rows per entry of a step's tile list
 
 
+def _check_sinks(sinks: Optional[torch.Tensor], n_heads: int) -> None:
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads or not sinks.is_contiguous()):
+        raise KernelError(f"attention: sinks must be contiguous float32 with {n_heads} entries")
+
+
 def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                      tok_seg: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                     page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
+                     page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
+                     sinks: Optional[torch.Tensor] = None) -> None:
     """One query token per request, bfloat16, tensor cores; a cluster of eight thread blocks per
-    (request, key/value head) shares the context and merges through distributed shared memory."""
-    need_cuda(q, cache, out, tables, tok_seg, pos)
+    (request, key/value head) shares the context and merges through distributed shared memory.  ``kv_stride`` 0 and
+    ``sinks``: as :func:`paged_attention`."""
+    need_cuda(q, cache, out, tables, tok_seg, pos, sinks)
+    _check_sinks(sinks, n_heads)
     need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
     need_contiguous("q", q), need_contiguous("out", out)
     n = q.shape[0]
@@ -549,7 +606,7 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ta
     _attention_mma.call("zi_decode_attention", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tok_seg), ptr(pos),
                         c_int(n), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
                         c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0),
-                        c_float(scale), stream())
+                        c_float(scale), ptr(sinks), stream())
 
 
 def decode_attention_split_from() -> int:
@@ -561,7 +618,7 @@ def decode_attention_split_from() -> int:
 def decode_attention_tma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                          tok_seg: Optional[torch.Tensor], pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                          page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
-                         max_kv_len: int = 0) -> None:
+                         max_kv_len: int = 0, sinks: Optional[torch.Tensor] = None) -> None:
     """One query token per request, bfloat16: the cluster kernel with 32-key tiles dealt to single warps, each
     fed by TMA through the block table into a ring of its own.  Same arguments as :func:`decode_attention`;
     head_dim 64 or 128, pages of a power of two from 8 to 128 tokens.  ``max_kv_len``: an upper bound of the cached
@@ -569,7 +626,8 @@ def decode_attention_tma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
     engine; the kernel then asks for its first page numbers without waiting for anything).  With few requests and long contexts several clusters then share one request's
     keys and a second kernel adds their parts (0: never).  A bounded wait that runs out is reported by
     :func:`tcgen05_status`."""
-    need_cuda(q, cache, out, tables, tok_seg, pos)
+    need_cuda(q, cache, out, tables, tok_seg, pos, sinks)
+    _check_sinks(sinks, n_heads)
     need_int32("tables", tables), need_int32("pos", pos)
     if tok_seg is not None:
         need_int32("tok_seg", tok_seg)
@@ -588,13 +646,14 @@ def decode_attention_tma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
                         ptr(_tc_status(q.device)), c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
                         c_int(page_size), c_int(tables.shape[1]), c_ll(cache.shape[0]), c_ll(page_stride), c_ll(kv_stride),
                         c_int(window or 0), c_float(scale), c_int(int(max_kv_len) if part_floats else 0), ptr(part),
-                        c_ll(part_floats), stream())
+                        c_ll(part_floats), ptr(sinks), stream())
     _tc_launched[q.device] = True
 
 
 def prefill_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                       tiles: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                      page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
+                      page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
+                      sinks: Optional[torch.Tensor] = None) -> None:
     """Portions of prompts, bfloat16, ``mma.sync`` tensor-core path.  ``tiles`` int32 ``[n_tiles, 3]``: (first token,
     rows <= 128, segment); the positions of a tile's tokens are consecutive.  Takes any page size and windows."""
     need_cuda(q, cache, out, tables, tiles, pos)
@@ -605,12 +664,13 @@ def prefill_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, t
     _attention_mma.call("zi_prefill_attention", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tiles), ptr(pos),
                         c_int(tiles.shape[0]), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
                         c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0),
-                        c_float(scale), stream())
+                        c_float(scale), ptr(sinks), stream())
 
 
 def prefill_attention_tcgen05(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                               tiles: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                              page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float) -> None:
+                              page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
+                              sinks: Optional[torch.Tensor] = None) -> None:
     """Portions of prompts, bfloat16, on tcgen05: scores and outputs accumulate in TMEM, K and V pages arrive by
     TMA through the block table.  Same arguments as :func:`prefill_attention`; head_dim 64 or 128, pages of a power
     of two from 8 to 128 tokens.  A bounded wait that runs out is reported by :func:`tcgen05_status`."""
@@ -622,12 +682,15 @@ def prefill_attention_tcgen05(q: torch.Tensor, cache: torch.Tensor, out: torch.T
     _attention_tcgen05.call("zi_prefill_attention_tcgen05", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tiles), ptr(pos),
                             ptr(_tc_status(q.device)), c_int(q.shape[0]), c_int(tiles.shape[0]), c_int(n_heads),
                             c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_int(tables.shape[1]),
-                            c_ll(cache.shape[0]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0), c_float(scale), stream())
+                            c_ll(cache.shape[0]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0), c_float(scale), ptr(sinks), stream())
     _tc_launched[q.device] = True
 
 
 def tcgen05_attention_ok(head_dim: int, page_size: int) -> bool:
     return head_dim in (64, 128) and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0
+
+
+LATENT_TENSOR_CORES = True       # one-plane caches and sinks on the tensor-core attention kernels (False: the general kernel)
 
 
 def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
@@ -637,37 +700,40 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
     Picks a kernel by dtype and by the shape of the step; all of them compute the same function.
     bfloat16 with head_dim 64 or 128 runs on the tensor cores: decode-only steps, and the single tokens at the head
     of a mixed step, on the cluster decode kernel, anything else on the tcgen05 prefill kernel (pages of 8..128 tokens) or the ``mma.sync`` prefill kernel (other
-    page sizes); float32 and other head sizes on the general kernel.
+    page sizes); float32 and other head sizes on the general kernel.  ``sinks`` (float32, one per query head) and a cache
+    with one plane (``cache.kv_stride`` 0, rows that are keys and values at once) are taken by every kernel.
     """
     tables = ctx.tables[cache.group]
-    if q.dtype == torch.bfloat16 and head_dim in (64, 128) and sinks is None and cache.kv_stride != 0:
+    if q.dtype == torch.bfloat16 and head_dim in (64, 128) and (LATENT_TENSOR_CORES or (sinks is None and cache.kv_stride != 0)):
         n = q.shape[0]
         if ctx.decode_only and tcgen05_attention_ok(head_dim, cache.page_size):
             # in a step of single tokens, token n is segment n
             decode_attention_tma(q, cache.tensor, out, tables, None, ctx.positions, n_heads, n_kv_heads, head_dim,
                                  cache.page_size, cache.page_stride, cache.kv_stride, window, scale,
-                                 max_kv_len=min(ctx.max_kv_len, window) if window else ctx.max_kv_len)
+                                 max_kv_len=min(ctx.max_kv_len, window) if window else ctx.max_kv_len, sinks=sinks)
             return
         if ctx.decode_only:
             decode_attention(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads, head_dim,
-                             cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+                             cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks)
             return
         tiles = ctx.extras.get("attn_tiles")
         lead = ctx.extras.get("leading_singles", 0) if tiles is not None else 0
         if lead:                                  # decoding requests beside a prompt portion: their own kernel
             if tcgen05_attention_ok(head_dim, cache.page_size):     # the leading single tokens are segments 0 .. lead - 1
                 decode_attention_tma(q[:lead], cache.tensor, out[:lead], tables, None, ctx.positions[:lead], n_heads,
-                                     n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+                                     n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale,
+                                     sinks=sinks)
             else:
                 decode_attention(q[:lead], cache.tensor, out[:lead], tables, ctx.tok_seg[:lead], ctx.positions[:lead], n_heads,
-                                 n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+                                 n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale,
+                                 sinks=sinks)
         if tiles is not None and tcgen05_attention_ok(head_dim, cache.page_size):
             prefill_attention_tcgen05(q, cache.tensor, out, tables, tiles, ctx.positions, n_heads, n_kv_heads, head_dim,
-                                      cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+                                      cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks)
             return
         if tiles is not None:
             prefill_attention(q, cache.tensor, out, tables, tiles, ctx.positions, n_heads, n_kv_heads, head_dim,
-                              cache.page_size, cache.page_stride, cache.kv_stride, window, scale)
+                              cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks)
             return
     paged_attention(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads,
                     head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks)

@@ -86,8 +86,7 @@ class SquaredReluMLP(FeedForward):
 
     def _activation(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         act = ctx.empty(x.shape[0], self.intermediate_size)
-        ops.linear(x, self.w_up, None, act)
-        ops.relu2(act, act)
+        ops.linear_relu2(x, self.w_up, act)               # the activation in the product's epilogue where it can be
         return act
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
@@ -126,10 +125,8 @@ class ClampedGatedMLP(FeedForward):
         self.w_down = tensors[self.down_name].contiguous()
 
     def _activation(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gate_up = ctx.empty(x.shape[0], 2 * self.intermediate_size)
-        ops.linear(x, self.w_gate_up, None, gate_up)
         act = ctx.empty(x.shape[0], self.intermediate_size)
-        ops.gated_clamp_mul(gate_up, act, self.limit, self.slope, self.up_offset)
+        ops.linear_gated_clamp_mul(x, self.w_gate_up, act, self.limit, self.slope, self.up_offset)
         return act
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
