@@ -215,9 +215,11 @@ def test_grouped_product_over_experts(rows, experts, top, tensor_cores, monkeypa
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rows", [1, 6, 90])
+@pytest.mark.parametrize("rows", [1, 6, 90, 700])
 @pytest.mark.parametrize("experts,top,shared", [(6, 2, True), (5, 1, False), (3, 3, True)])
 def test_routed_feed_forward_part(dtype, rows, experts, top, shared):
+    """700 rows in bfloat16: the grouped products run on the tcgen05 kernel over rows copied into sorted order, every
+    expert's share padded to whole tiles; fewer rows, and float32: the kernels of ``csrc/moe.cu``."""
     from zedinfer_b200.config import PartSpec
     from zedinfer_b200.parts import RoutedExperts
     sh = PartSpec("clamped_gated_mlp", {"hidden_size": 64, "intermediate_size": 24, "limit": 0.6, "slope": 1.702,
@@ -237,6 +239,42 @@ def test_routed_feed_forward_part(dtype, rows, experts, top, shared):
     pidx, pw = BP.route(x.double(), w["router"], w["router.b"], top)
     assert torch.equal(idx.cpu().long(), pidx) and rel_err(wts, pw) < 1e-5
     assert rel_err(got, want) < (2e-5 if dtype == torch.float32 else 4e-2)
+    from zedinfer_b200 import ops
+    assert ff._tcgen05_ok(x.to(DEV), rows * top) == (dtype == torch.bfloat16 and rows * top >= ops.MOE_TCGEN05_MIN_PAIRS)
+    ops.raise_if_tcgen05_failed(torch.device(DEV))
+
+
+def test_padded_grouping_leaves_whole_tiles_to_every_expert():
+    from zedinfer_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    experts, top, rows, pad = 7, 2, 333, 128
+    idx = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(rows)]).int()
+    idx[idx == 4] = 5                                   # expert 4 gets nothing
+    pairs = rows * top
+    tiles = (pairs + experts * (pad - 1) + pad - 1) // pad
+    starts = torch.empty(experts + 1, dtype=torch.int32, device=DEV)
+    row_pair = torch.empty(tiles * pad, dtype=torch.int32, device=DEV)
+    pair_row = torch.empty(pairs, dtype=torch.int32, device=DEV)
+    tile_expert = torch.empty(tiles, dtype=torch.int32, device=DEV)
+    ops.moe_group_padded(idx.to(DEV), experts, pad, starts, row_pair, pair_row, tile_expert)
+    counts = torch.bincount(idx.flatten().long(), minlength=experts)
+    want_starts = [0]
+    for c in counts.tolist():
+        want_starts.append(want_starts[-1] + -(-c // pad) * pad)
+    assert starts.tolist() == want_starts
+    rp, pr, te = row_pair.cpu().long(), pair_row.cpu().long(), tile_expert.tolist()
+    assert torch.equal(rp[pr], torch.arange(pairs)) and int((rp >= 0).sum()) == pairs
+    flat = idx.flatten().long()
+    for e in range(experts):
+        mine = rp[want_starts[e]:want_starts[e + 1]]
+        assert int((mine >= 0).sum()) == int(counts[e]) and all(int(flat[p]) == e for p in mine[mine >= 0].tolist())
+        assert te[want_starts[e] // pad:want_starts[e + 1] // pad] == [e] * ((want_starts[e + 1] - want_starts[e]) // pad)
+    assert all(t == -1 for t in te[want_starts[-1] // pad:])
+    x = torch.randn(rows, 40, generator=g).bfloat16().to(DEV)
+    out = torch.empty(tiles * pad, 40, dtype=torch.bfloat16, device=DEV)
+    ops.moe_gather_rows(x, row_pair, top, out)
+    ref = torch.where((rp >= 0)[:, None], x.cpu()[(rp.clamp(min=0) // top)], torch.zeros(1, 40, dtype=torch.bfloat16))
+    assert torch.equal(out.cpu(), ref)
 
 
 def write_latents(view, tables, c):

@@ -183,6 +183,11 @@ struct TpParams {
     int bn;                     // accumulator columns per tile
     int up_row0;                // silu_mul: first row of the up half in W
     int tiles_m, tiles_n;
+    // Grouped product (several weights stacked in W, one per group of 128-row tiles of X): tile_expert[mt] is the
+    // weight of row tile mt, or -1 for a row tile that holds nothing (skipped by every role); expert_rows the rows of W
+    // per weight.  Null: the plain product.
+    const int* tile_expert;
+    int expert_rows;
 };
 
 __device__ __forceinline__ void tp_store16(const TpParams& p, long long base, int n, const float (&v)[16]) {
@@ -309,8 +314,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const int m0 = (tile % p.tiles_m) * TC_BM, nt = tile / p.tiles_m;
-            const int row_b0 = p.silu_mul ? nt * half : nt * p.bn;
-            const int row_b1 = p.silu_mul ? p.up_row0 + nt * half : nt * p.bn + half;
+            int w0 = 0;                                     // first row of this tile's weight in W
+            if (p.tile_expert) {
+                const int e = p.tile_expert[tile % p.tiles_m];
+                if (e < 0) continue;
+                w0 = e * p.expert_rows;
+            }
+            const int row_b0 = w0 + (p.silu_mul ? nt * half : nt * p.bn);
+            const int row_b1 = w0 + (p.silu_mul ? p.up_row0 + nt * half : nt * p.bn + half);
             for (int kb = 0; kb < k_blocks; ++kb, ++kbg) {
                 const uint32_t s = kbg % TP_STAGES;
                 if (kbg >= TP_STAGES && !mbar_wait_warp(empty0 + 8 * s, ((kbg / TP_STAGES) - 1) & 1, &gave_up)) {
@@ -340,9 +351,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         uint32_t kbg = 0;
         bool ok = true;
         int it = 0;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            if (p.tile_expert && p.tile_expert[tile % p.tiles_m] < 0) continue;      // `it` counts the tiles that are worked on
             const uint32_t buf = it & 1;
-            if (it >= 2 && !mbar_wait_warp(tempty0 + 8 * buf, ((it >> 1) - 1) & 1, &gave_up)) {
+            ++it;
+            if (it > 2 && !mbar_wait_warp(tempty0 + 8 * buf, (((it - 1) >> 1) - 1) & 1, &gave_up)) {
                 if (lane == 0) { atomicExch(p.status, 4); gave_up = 1; }
                 break;
             }
@@ -370,9 +383,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     } else {
         const int quad = warp & 3;
         int it = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            if (p.tile_expert && p.tile_expert[tile % p.tiles_m] < 0) continue;
             const uint32_t buf = it & 1;
-            const bool ok = __all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, (it >> 1) & 1, &gave_up));
+            const int phase = (it >> 1) & 1;
+            ++it;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * buf, phase, &gave_up));
             if (!ok) { if (lane == 0) { atomicExch(p.status, 3); gave_up = 1; } break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int m = (tile % p.tiles_m) * TC_BM + quad * 32 + lane, nt = tile / p.tiles_m;
@@ -617,7 +633,7 @@ ZI_EXPORT int zi_gemm_tcgen05_tiles(const void* X, const void* W, const void* bi
     if (bn < step || bn > 256 || bn % step) return zi_fail("gemm_tcgen05: tile width %d must be a multiple of %d up to 256", bn, step);
     TpParams p;
     p.C = C; p.bias = (const bf16*)bias; p.status = status; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
-    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = gated ? 1 : 0; p.act = epilogue; p.act_limit = act_limit; p.act_slope = act_slope; p.act_offset = act_offset; p.bn = bn; p.up_row0 = N;
+    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = gated ? 1 : 0; p.act = epilogue; p.act_limit = act_limit; p.act_slope = act_slope; p.act_offset = act_offset; p.bn = bn; p.up_row0 = N; p.tile_expert = nullptr; p.expert_rows = 0;
     p.tiles_m = tiles_m;
     const int cols = gated ? bn / 2 : bn;
     p.tiles_n = (N + cols - 1) / cols;
@@ -635,6 +651,56 @@ ZI_EXPORT int zi_gemm_tcgen05_tiles(const void* X, const void* W, const void* bi
     const int grid = (int)(n_tiles < num_sms ? n_tiles : num_sms);
     gemm_tcgen05_persistent_kernel<<<grid, TC_THREADS, TP_SMEM, stream>>>(ma, mb, p);
     return zi_check_launch("gemm_tcgen05_persistent");
+}
+
+// The grouped product: X holds the rows of every group one after the other, each group padded to whole 128-row
+// tiles (M rows in all, a multiple of 128); W stacks one weight per group, [n_experts * rows_per_expert, K] with
+// rows_per_expert = N (2 N with the gated epilogues 1 and 2); tile_expert[M / 128] on the device says which weight a
+// row tile takes, -1 for a row tile that holds nothing.  C[M, N] row by row as X.  Epilogues as zi_gemm_tcgen05_tiles.
+ZI_EXPORT int zi_gemm_tcgen05_grouped(const void* X, const void* W, void* C, int c_dtype, int* status, int M, int N, int K,
+                                      long long ldx, long long ldc, int epilogue, int n_experts, const int* tile_expert,
+                                      int num_sms, float act_limit, float act_slope, float act_offset, cudaStream_t stream) {
+    const bool gated = epilogue == 1 || epilogue == 2;
+    if (M <= 0 || N <= 0) return 0;
+    if (M % TC_BM) return zi_fail("gemm_tcgen05_grouped: M=%d must be a multiple of %d", M, TC_BM);
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0) return zi_fail("gemm_tcgen05_grouped: K=%d and ldx=%lld must be positive multiples of 8", K, ldx);
+    if (((uintptr_t)X | (uintptr_t)W) & 15) return zi_fail("gemm_tcgen05_grouped: operands must be 16-byte aligned");
+    if (c_dtype != ZI_F32 && c_dtype != ZI_BF16) return zi_fail("gemm_tcgen05_grouped: unknown output dtype %d", c_dtype);
+    if (epilogue < 0 || epilogue > 3) return zi_fail("gemm_tcgen05_grouped: unknown epilogue %d", epilogue);
+    if (!status || !tile_expert || n_experts <= 0 || num_sms <= 0) return zi_fail("gemm_tcgen05_grouped: status, tile_expert, experts and num_sms are required");
+    if (tc_init()) return 1;
+    const int step = gated ? 32 : 16;
+    const int tiles_m = M / TC_BM;
+    int bn = 0;
+    long long best = -1;
+    for (int cand = 256; cand >= step; cand -= step) {
+        const int cols = gated ? cand / 2 : cand;
+        const long long tiles = (long long)tiles_m * ((N + cols - 1) / cols);
+        const long long cost = ((tiles + num_sms - 1) / num_sms) * tp_step_cost(cand);
+        if (best < 0 || cost < best) { best = cost; bn = cand; }
+    }
+    TpParams p;
+    p.C = C; p.bias = nullptr; p.status = status; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
+    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = gated ? 1 : 0; p.act = epilogue; p.act_limit = act_limit; p.act_slope = act_slope;
+    p.act_offset = act_offset; p.bn = bn; p.up_row0 = N;
+    p.expert_rows = gated ? 2 * N : N; p.tile_expert = tile_expert;
+    p.tiles_m = tiles_m;
+    const int cols = gated ? bn / 2 : bn;
+    p.tiles_n = (N + cols - 1) / cols;
+    const long long n_tiles = (long long)p.tiles_m * p.tiles_n;
+    if (n_tiles > 0x7fffffffLL) return zi_fail("gemm_tcgen05_grouped: too many tiles");
+    CUtensorMap ma, mb;
+    if (tc_make_map(&ma, X, M, K, ldx, TC_BM)) return 1;
+    if (tc_make_map(&mb, W, (long long)n_experts * p.expert_rows, K, K, bn / 2)) return 1;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TP_SMEM);
+        if (e != cudaSuccess) return zi_fail("gemm_tcgen05_grouped: cannot reserve %zu bytes of shared memory: %s", TP_SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    const int grid = (int)(n_tiles < num_sms ? n_tiles : num_sms);
+    gemm_tcgen05_persistent_kernel<<<grid, TC_THREADS, TP_SMEM, stream>>>(ma, mb, p);
+    return zi_check_launch("gemm_tcgen05_grouped");
 }
 
 static int tq_step_cost(int bn) { const int pipe = bn / 2, smem = 32 + bn / 8; return pipe > smem ? pipe : smem; }
@@ -687,7 +753,7 @@ ZI_EXPORT int zi_gemm_tcgen05_pairs(const void* X, const void* W, const void* bi
     if (bn < step || bn > 256 || bn % step) return zi_fail("gemm_tcgen05: tile width %d must be a multiple of %d up to 256", bn, step);
     TpParams p;
     p.C = C; p.bias = (const bf16*)bias; p.status = status; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
-    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = gated ? 1 : 0; p.act = epilogue; p.act_limit = act_limit; p.act_slope = act_slope; p.act_offset = act_offset; p.bn = bn; p.up_row0 = N;
+    p.c_is_f32 = c_dtype == ZI_F32; p.silu_mul = gated ? 1 : 0; p.act = epilogue; p.act_limit = act_limit; p.act_slope = act_slope; p.act_offset = act_offset; p.bn = bn; p.up_row0 = N; p.tile_expert = nullptr; p.expert_rows = 0;
     p.tiles_m = tiles_m;
     const int cols = gated ? bn / 2 : bn;
     p.tiles_n = (N + cols - 1) / cols;

@@ -108,6 +108,79 @@ ZI_EXPORT int zi_moe_group(const int* idx, int n_pairs, int n_experts, int* offs
     return zi_check_launch("moe_group");
 }
 
+// Grouping with every expert's rows padded to a multiple of `pad` (the row tile of the tcgen05 grouped product):
+// starts[e] is the first sorted row of expert e (a multiple of pad), row_pair[r] the pair at sorted row r or -1 for a
+// row of padding, pair_row its inverse, tile_expert[t] the expert of row tile t or -1 behind the last one.
+// row_pair has n_rows_max = tiles_max * pad entries, tile_expert tiles_max.
+__global__ void __launch_bounds__(GROUP_THREADS)
+moe_group_padded_kernel(const int* __restrict__ idx, int n_pairs, int n_experts, int pad, int tiles_max,
+                        int* __restrict__ starts, int* __restrict__ row_pair, int* __restrict__ pair_row,
+                        int* __restrict__ tile_expert) {
+    extern __shared__ int sh[];                 // counts[E], then cursors[E]
+    int* counts = sh;
+    int* cursor = sh + n_experts;
+    for (int e = threadIdx.x; e < n_experts; e += GROUP_THREADS) counts[e] = 0;
+    for (int r = threadIdx.x; r < tiles_max * pad; r += GROUP_THREADS) row_pair[r] = -1;
+    for (int t = threadIdx.x; t < tiles_max; t += GROUP_THREADS) tile_expert[t] = -1;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += GROUP_THREADS) atomicAdd(&counts[idx[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            starts[e] = run;
+            cursor[e] = run;
+            const int tiles = (counts[e] + pad - 1) / pad;
+            for (int t = 0; t < tiles; ++t) tile_expert[run / pad + t] = e;
+            run += tiles * pad;
+        }
+        starts[n_experts] = run;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += GROUP_THREADS) {
+        const int r = atomicAdd(&cursor[idx[p]], 1);
+        row_pair[r] = p;
+        pair_row[p] = r;
+    }
+}
+
+ZI_EXPORT int zi_moe_group_padded(const int* idx, int n_pairs, int n_experts, int pad, int tiles_max, int* starts,
+                                  int* row_pair, int* pair_row, int* tile_expert, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    if (n_experts <= 0 || n_experts > 4096 || pad <= 0) return zi_fail("moe_group: %d experts, pad %d", n_experts, pad);
+    if ((long long)tiles_max * pad < (long long)n_pairs + (long long)n_experts * (pad - 1))
+        return zi_fail("moe_group: %d tiles of %d rows cannot hold %d pairs of %d experts", tiles_max, pad, n_pairs, n_experts);
+    moe_group_padded_kernel<<<1, GROUP_THREADS, 2 * n_experts * sizeof(int), stream>>>(idx, n_pairs, n_experts, pad, tiles_max,
+                                                                                      starts, row_pair, pair_row, tile_expert);
+    return zi_check_launch("moe_group_padded");
+}
+
+// Rows of x brought into sorted order: out[r, :] = x[row_pair[r] / pairs_per_src, :], zeros for a row of padding.
+// bfloat16, K % 8 == 0, 16-byte aligned rows.
+__global__ void moe_gather_rows_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ row_pair,
+                                       int pairs_per_src, bf16* __restrict__ out, int n_rows, int k8) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)n_rows * k8;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / k8), c = (int)(i - (long long)r * k8);
+        const int pair = row_pair[r];
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (pair >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)(pair / pairs_per_src) * ldx + c * 8);
+        *reinterpret_cast<uint4*>(out + (size_t)r * k8 * 8 + c * 8) = v;
+    }
+}
+
+ZI_EXPORT int zi_moe_gather_rows(const void* x, long long ldx, const int* row_pair, int pairs_per_src, void* out, int n_rows,
+                                 int K, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (K <= 0 || K % 8 || ldx % 8 || (((uintptr_t)x | (uintptr_t)out) & 15) || pairs_per_src <= 0)
+        return zi_fail("moe_gather_rows: K=%d and the rows must be multiples of 8 elements and 16-byte aligned", K);
+    const long long total = (long long)n_rows * (K / 8);
+    const long long want = (total + 255) / 256;
+    moe_gather_rows_kernel<<<(int)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>((const bf16*)x, ldx, row_pair, pairs_per_src,
+                                                                                       (bf16*)out, n_rows, K / 8);
+    return zi_check_launch("moe_gather_rows");
+}
+
 // ---------------------------------------------------------------------------------------
 // Grouped product.  Sorted row r belongs to expert e with offsets[e] <= r < offsets[e + 1]; its A row is
 // A[src, :] with src = row_pair[r] / pairs_per_src (row_pair null: src = r).  W is [E, N_w, K].

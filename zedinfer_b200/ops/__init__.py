@@ -33,7 +33,8 @@ SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "rope_table", "gemm_smallm_rope", "can_fuse_rope_product", "silu_mul", "add", "cast",
            "gemm_nt", "linear", "linear_for_residual", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode",
            "embedding_positions", "softcap", "relu2", "gated_clamp_mul", "rmsnorm_append", "linear_per_head", "route_topk",
-           "moe_group", "moe_gemm", "moe_combine", "linear_gated_clamp_mul", "linear_relu2"]
+           "moe_group", "moe_gemm", "moe_combine", "linear_gated_clamp_mul", "linear_relu2", "moe_group_padded",
+           "moe_gather_rows", "gemm_tcgen05_grouped"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -941,7 +942,62 @@ def moe_group(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, row_pair
     _moe.call("zi_moe_group", ptr(idx), c_int(pairs), c_int(n_experts), ptr(offsets), ptr(row_pair), ptr(pair_row), stream())
 
 
+def moe_group_padded(idx: torch.Tensor, n_experts: int, pad: int, starts: torch.Tensor, row_pair: torch.Tensor,
+                     pair_row: torch.Tensor, tile_expert: torch.Tensor) -> None:
+    """As :func:`moe_group` with every expert's rows padded to whole tiles of ``pad`` rows: ``starts`` (int32
+    ``[experts + 1]``), ``row_pair`` (``[tiles * pad]``, -1 for a row of padding), ``pair_row`` and ``tile_expert``
+    (``[tiles]``: the expert of a row tile, -1 behind the last); ``tiles * pad >= pairs + experts * (pad - 1)``."""
+    need_cuda(idx, starts, row_pair, pair_row, tile_expert)
+    for name, t in (("idx", idx), ("starts", starts), ("row_pair", row_pair), ("pair_row", pair_row), ("tile_expert", tile_expert)):
+        need_int32(name, t), need_contiguous(name, t)
+    tiles = tile_expert.numel()
+    if starts.numel() != n_experts + 1 or row_pair.numel() != tiles * pad or pair_row.numel() != idx.numel():
+        raise KernelError("moe_group_padded: starts [experts + 1], row_pair [tiles * pad], pair_row one entry per pair")
+    _moe.call("zi_moe_group_padded", ptr(idx), c_int(idx.numel()), c_int(n_experts), c_int(pad), c_int(tiles), ptr(starts),
+              ptr(row_pair), ptr(pair_row), ptr(tile_expert), stream())
+
+
+def moe_gather_rows(x: torch.Tensor, row_pair: torch.Tensor, pairs_per_src: int, out: torch.Tensor) -> None:
+    """``out[r] = x[row_pair[r] // pairs_per_src]``, zeros where ``row_pair[r]`` is negative (bfloat16)."""
+    need_cuda(x, row_pair, out)
+    need_int32("row_pair", row_pair), need_contiguous("out", out)
+    if x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or x.stride(1) != 1 or out.shape != (row_pair.numel(), x.shape[1]):
+        raise KernelError(f"moe_gather_rows: x {tuple(x.shape)} {x.dtype}, out {tuple(out.shape)}, {row_pair.numel()} rows")
+    _moe.call("zi_moe_gather_rows", ptr(x), c_ll(x.stride(0)), ptr(row_pair), c_int(pairs_per_src), ptr(out), c_int(out.shape[0]),
+              c_int(x.shape[1]), stream())
+
+
+GROUPED_TILE_ROWS = 128          # rows of a tile of the tcgen05 grouped product: groups are padded to whole tiles
+
+
+def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor,
+                         gated: Optional[tuple] = None) -> None:
+    """Grouped product on the tcgen05 tensor cores: ``x`` holds every group's rows one after the other, padded to
+    whole tiles of 128 rows; row tile t takes the weight ``w[tile_expert[t]]`` (``w`` is ``[experts, N, K]``, or with
+    ``gated = (limit, slope, up_offset)`` ``[experts, 2 N, K]`` and the clamped, gated activation in the epilogue); a
+    negative entry skips the tile.  ``out [rows, N]`` row by row as ``x``.  A bounded wait that runs out is reported by
+    :func:`tcgen05_status`."""
+    need_cuda(x, w, tile_expert, out)
+    need_int32("tile_expert", tile_expert)
+    need_contiguous("w", w), need_contiguous("tile_expert", tile_expert)
+    m, k = x.shape
+    e, n_w, _ = w.shape
+    n = out.shape[1]
+    if (m % GROUPED_TILE_ROWS or tile_expert.numel() != m // GROUPED_TILE_ROWS or w.shape[2] != k or out.shape[0] != m
+            or n_w != (2 * n if gated else n) or x.stride(1) != 1 or out.stride(1) != 1):
+        raise KernelError(f"gemm_tcgen05_grouped: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, "
+                          f"{tile_expert.numel()} tiles do not agree")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_tcgen05_grouped: bfloat16 operands only")
+    limit, slope, up_offset = gated if gated else (0.0, 0.0, 0.0)
+    _gemm_tcgen05.call("zi_gemm_tcgen05_grouped", ptr(x), ptr(w), ptr(out), c_int(dtype_code(out.dtype)), ptr(_tc_status(x.device)),
+                       c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(out.stride(0)), c_int(2 if gated else 0), c_int(e),
+                       ptr(tile_expert), c_int(_num_sms(x.device)), c_float(limit), c_float(slope), c_float(up_offset), stream())
+    _tc_launched[x.device] = True
+
+
 MOE_TENSOR_CORES = True          # bfloat16 grouped products on the tensor cores (False: the SIMT form, as float32 uses)
+MOE_TCGEN05_MIN_PAIRS = 512      # from this many (token, choice) pairs the grouped products run on the tcgen05 kernel
 
 
 def moe_gemm(a: torch.Tensor, row_pair: Optional[torch.Tensor], pairs_per_src: int, w: torch.Tensor, offsets: torch.Tensor,
@@ -968,13 +1024,14 @@ def moe_gemm(a: torch.Tensor, row_pair: Optional[torch.Tensor], pairs_per_src: i
 
 def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, wts: torch.Tensor, shared: Optional[torch.Tensor],
                 out: torch.Tensor) -> None:
-    """``out[t] = sum_j wts[t, j] * y[pair_row[t, j]] (+ shared[t])``, j rising, in float32 with one rounding."""
+    """``out[t] = sum_j wts[t, j] * y[pair_row[t, j]] (+ shared[t])``, j rising, in float32 with one rounding.  ``y`` has
+    a row per pair, or more where the sorted rows are padded."""
     need_cuda(y, pair_row, wts, shared, out)
     need_int32("pair_row", pair_row)
     need_contiguous("y", y), need_contiguous("pair_row", pair_row), need_contiguous("wts", wts), need_contiguous("out", out)
     n, hidden = out.shape
     top = wts.shape[1]
-    if wts.dtype != torch.float32 or wts.shape != (n, top) or pair_row.numel() != n * top or y.shape != (n * top, hidden) \
+    if wts.dtype != torch.float32 or wts.shape != (n, top) or pair_row.numel() != n * top or y.dim() != 2 or y.shape[0] < n * top or y.shape[1] != hidden \
             or y.dtype != out.dtype or (shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype
                                                                 or not shared.is_contiguous())):
         raise KernelError(f"moe_combine: y {tuple(y.shape)}, wts {tuple(wts.shape)}, out {tuple(out.shape)} do not agree")

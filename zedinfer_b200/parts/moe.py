@@ -89,6 +89,8 @@ class RoutedExperts(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         n, pairs = x.shape[0], x.shape[0] * self.top
         idx, wts = self.route(x)
+        if self._tcgen05_ok(x, pairs):
+            return self._forward_tcgen05(x, ctx, idx, wts)
         offsets = torch.empty(self.experts + 1, dtype=torch.int32, device=x.device)
         row_pair = torch.empty(pairs, dtype=torch.int32, device=x.device)
         pair_row = torch.empty(pairs, dtype=torch.int32, device=x.device)
@@ -97,6 +99,33 @@ class RoutedExperts(FeedForward):
         ops.moe_gemm(x, row_pair, self.top, self.w_gate_up, offsets, act, gated=(self.limit, self.slope, self.up_offset))
         y = ctx.empty(pairs, self.hidden_size)
         ops.moe_gemm(act, None, 1, self.w_down, offsets, y)
+        shared = self.shared.forward(x, ctx) if self.shared is not None else None
+        out = ctx.empty(n, self.hidden_size)
+        ops.moe_combine(y, pair_row, wts, shared, out)
+        return out
+
+    def _tcgen05_ok(self, x: torch.Tensor, pairs: int) -> bool:
+        return (ops.MOE_TENSOR_CORES and pairs >= ops.MOE_TCGEN05_MIN_PAIRS and x.dtype == torch.bfloat16
+                and self.w_gate_up.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.intermediate_size % 8 == 0
+                and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+
+    def _forward_tcgen05(self, x: torch.Tensor, ctx: StepContext, idx: torch.Tensor, wts: torch.Tensor) -> torch.Tensor:
+        """Many rows: the step's rows are copied into sorted order, every expert's share padded to whole 128-row
+        tiles, and both products run on the tcgen05 grouped kernel (the activation in the first one's epilogue)."""
+        n, pairs, pad = x.shape[0], x.shape[0] * self.top, ops.GROUPED_TILE_ROWS
+        tiles = (pairs + self.experts * (pad - 1) + pad - 1) // pad
+        dev = x.device
+        starts = torch.empty(self.experts + 1, dtype=torch.int32, device=dev)
+        row_pair = torch.empty(tiles * pad, dtype=torch.int32, device=dev)
+        pair_row = torch.empty(pairs, dtype=torch.int32, device=dev)
+        tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
+        ops.moe_group_padded(idx, self.experts, pad, starts, row_pair, pair_row, tile_expert)
+        xs = ctx.empty(tiles * pad, self.hidden_size)
+        ops.moe_gather_rows(x, row_pair, self.top, xs)
+        act = ctx.empty(tiles * pad, self.intermediate_size)
+        ops.gemm_tcgen05_grouped(xs, self.w_gate_up, tile_expert, act, gated=(self.limit, self.slope, self.up_offset))
+        y = ctx.empty(tiles * pad, self.hidden_size)
+        ops.gemm_tcgen05_grouped(act, self.w_down, tile_expert, y)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         out = ctx.empty(n, self.hidden_size)
         ops.moe_combine(y, pair_row, wts, shared, out)
