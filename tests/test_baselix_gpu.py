@@ -173,12 +173,15 @@ def test_router_top_choices_and_their_weights():
     assert idx.tolist() == [[1, 2]] and wts.tolist() == [[0.5, 0.5]]
 
 
+@pytest.mark.parametrize("streaming", [False, True])
 @pytest.mark.parametrize("tensor_cores", [False, True])
-@pytest.mark.parametrize("rows,experts,top", [(1, 4, 2), (9, 6, 2), (200, 5, 1), (70, 3, 3)])
-def test_grouped_product_over_experts(rows, experts, top, tensor_cores, monkeypatch):
-    """The grouped product alone, both forms, against one product per row; experts without rows among them."""
+@pytest.mark.parametrize("rows,experts,top", [(1, 4, 2), (9, 6, 2), (200, 5, 1), (70, 3, 3), (30, 4, 2)])
+def test_grouped_product_over_experts(rows, experts, top, tensor_cores, streaming, monkeypatch):
+    """The grouped product alone against one product per row, experts without rows among them: the weight-streaming
+    form (up to 64 sorted rows), the ``wmma`` form (bfloat16) and the SIMT form (float32, and what the others leave)."""
     from zedinfer_b200 import ops
     monkeypatch.setattr(ops, "MOE_TENSOR_CORES", tensor_cores)
+    monkeypatch.setattr(ops, "MOE_FEW_ROWS_STREAMING", streaming)
     dtype = torch.bfloat16 if tensor_cores else torch.float32
     g = torch.Generator().manual_seed(rows)
     k, n = 72, 40
@@ -241,6 +244,7 @@ def test_routed_feed_forward_part(dtype, rows, experts, top, shared):
     assert rel_err(got, want) < (2e-5 if dtype == torch.float32 else 4e-2)
     from zedinfer_b200 import ops
     assert ff._tcgen05_ok(x.to(DEV), rows * top) == (dtype == torch.bfloat16 and rows * top >= ops.MOE_TCGEN05_MIN_PAIRS)
+    assert ops.MOE_TCGEN05_MIN_PAIRS <= 90 * 2
     ops.raise_if_tcgen05_failed(torch.device(DEV))
 
 

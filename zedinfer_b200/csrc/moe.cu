@@ -70,6 +70,95 @@ ZI_EXPORT int zi_route_topk(const float* logits, int n_tokens, int n_experts, in
 }
 
 // ---------------------------------------------------------------------------------------
+// The router in one kernel: logits z[e] = x . Wr[e] + b[e] in float32 (x and Wr of any storage type), the `top`
+// largest and the softmax over them.  One block per token: the row of x waits in shared memory as float32, every
+// warp takes experts w, w + 4, ...; a lane's partial sum runs over k in rising order and the warp adds the lanes in a
+// fixed order, so a token's logits depend on nothing else in the step.  Then the first warp chooses as
+// route_topk_kernel does.
+// ---------------------------------------------------------------------------------------
+#define RF_WARPS 4
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(RF_WARPS * 32)
+route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict__ w, const float* __restrict__ bias,
+                   int K, int n_experts, int top, int* __restrict__ idx, float* __restrict__ wts,
+                   float* __restrict__ logits_out) {
+    extern __shared__ float rf_smem[];              // x row [K], then logits [n_experts]
+    float* xs = rf_smem;
+    float* z = rf_smem + K;
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TX* xr = x + (size_t)t * ldx;
+    for (int k = threadIdx.x; k < K; k += RF_WARPS * 32) xs[k] = to_f32<TX>(xr[k]);
+    __syncthreads();
+    for (int e = warp; e < n_experts; e += RF_WARPS) {
+        const TW* wr = w + (size_t)e * K;
+        float acc = 0.0f;
+        if (K % 8 == 0 && (((uintptr_t)wr) & (sizeof(TW) * 8 - 1)) == 0) {
+            for (int k = lane * 8; k < K; k += 256) {
+                float wv[8];
+                load8(wr + k, wv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc = fmaf(xs[k + i], wv[i], acc);
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], to_f32<TW>(wr[k]), acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const float v = acc + (bias ? bias[e] : 0.0f);
+            z[e] = v;
+            if (logits_out) logits_out[(size_t)t * n_experts + e] = v;
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float first = 0.0f, denom = 0.0f;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (j == 0) first = best;
+        const float p = expf(best - first);
+        denom += p;
+        if (lane == 0) {
+            idx[(size_t)t * top + j] = best_e;
+            wts[(size_t)t * top + j] = p;
+            z[best_e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0)
+        for (int j = 0; j < top; ++j) wts[(size_t)t * top + j] = wts[(size_t)t * top + j] / denom;
+}
+
+// logits_out: optional float32 [n_tokens, n_experts] (tests).  bias: float32 or null.
+ZI_EXPORT int zi_route(const void* x, int x_dtype, long long ldx, const void* w, int w_dtype, const float* bias, int n_tokens,
+                       int K, int n_experts, int top, int* idx, float* wts, float* logits_out, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (K <= 0 || n_experts <= 0 || n_experts > 4096) return zi_fail("route: K=%d experts=%d", K, n_experts);
+    if (top <= 0 || top > n_experts) return zi_fail("route: top=%d of %d experts", top, n_experts);
+    const size_t smem = ((size_t)K + n_experts) * sizeof(float);
+    if (smem > 200 * 1024) return zi_fail("route: a row of %d values and %d logits do not fit shared memory", K, n_experts);
+    ZI_DISPATCH(x_dtype, TX, ZI_DISPATCH(w_dtype, TW, {
+        auto fn = route_fused_kernel<TX, TW>;
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return zi_fail("route: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        }
+        fn<<<n_tokens, RF_WARPS * 32, smem, stream>>>((const TX*)x, ldx, (const TW*)w, bias, K, n_experts, top, idx, wts, logits_out);
+    }););
+    return zi_check_launch("route");
+}
+
+// ---------------------------------------------------------------------------------------
 // Grouping: one block.  offsets[e] .. offsets[e + 1] are the sorted rows of expert e.
 // ---------------------------------------------------------------------------------------
 #define GROUP_THREADS 1024
@@ -311,6 +400,85 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restr
     }
 }
 
+// Few rows (decode steps): the product is bound by reading every used expert's weight once.  A block takes one
+// expert and eight output columns, a warp one column: it streams that column's weight row (and, gated, the up row
+// that pairs with it) with 16-byte loads, six or more in flight per lane, against up to GV_ROWS of the expert's rows of
+// A that wait in shared memory as float32; float32 FMAs, lanes added in a fixed order.  An expert with more rows
+// takes them GV_ROWS at a time (its weight rows then come from L2).  Experts without rows cost an empty block.
+#define GV_ROWS 4
+#define GV_WARPS 8
+template <typename TA, typename TW, typename TC, bool GATED>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ row_pair, int pairs_per_src,
+                const TW* __restrict__ W, const int* __restrict__ offsets, TC* __restrict__ C, long long ldc, int N, int K,
+                float limit, float slope, float up_offset) {
+    extern __shared__ __align__(16) float gv_x[];                 // [GV_ROWS][K]
+    const int e = blockIdx.y, lo = offsets[e], hi = offsets[e + 1];
+    if (lo >= hi) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * GV_WARPS + warp;
+    const TW* wg = W + ((size_t)e * (GATED ? 2 * N : N) + (n < N ? n : 0)) * K;
+    const TW* wu = wg + (size_t)N * K;
+    const bool vec = K % 8 == 0 && ((((uintptr_t)W) & 31) == 0);
+    for (int r0 = lo; r0 < hi; r0 += GV_ROWS) {
+        const int rows = hi - r0 < GV_ROWS ? hi - r0 : GV_ROWS;
+        __syncthreads();
+        for (int i = threadIdx.x; i < GV_ROWS * K; i += GV_WARPS * 32) {
+            const int r = i / K, k = i - r * K;
+            float v = 0.0f;
+            if (r < rows) {
+                const int src = row_pair ? row_pair[r0 + r] / pairs_per_src : r0 + r;
+                v = to_f32<TA>(A[(size_t)src * lda + k]);
+            }
+            gv_x[i] = v;
+        }
+        __syncthreads();
+        if (n >= N) continue;
+        float ag[GV_ROWS], au[GV_ROWS];
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) ag[r] = au[r] = 0.0f;
+        if (vec) {
+            for (int k = lane * 8; k < K; k += 256) {
+                float wv[8], uv[8];
+                load8(wg + k, wv);
+                if (GATED) load8(wu + k, uv);
+#pragma unroll
+                for (int r = 0; r < GV_ROWS; ++r) {
+                    const float4 x0 = *reinterpret_cast<const float4*>(gv_x + r * K + k);
+                    const float4 x1 = *reinterpret_cast<const float4*>(gv_x + r * K + k + 4);
+                    const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        ag[r] = fmaf(xv[i], wv[i], ag[r]);
+                        if (GATED) au[r] = fmaf(xv[i], uv[i], au[r]);
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) {
+                const float wv = to_f32<TW>(wg[k]), uv = GATED ? to_f32<TW>(wu[k]) : 0.0f;
+#pragma unroll
+                for (int r = 0; r < GV_ROWS; ++r) {
+                    ag[r] = fmaf(gv_x[r * K + k], wv, ag[r]);
+                    if (GATED) au[r] = fmaf(gv_x[r * K + k], uv, au[r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) {
+            float g = warp_sum(ag[r]);
+            float u = GATED ? warp_sum(au[r]) : 0.0f;
+            if (lane == 0 && r < rows) {
+                if (GATED) {
+                    // the two halves are rounded to the storage type first, as a separate product would have stored them
+                    g = clamped_gate(to_f32<TC>(from_f32<TC>(g)), to_f32<TC>(from_f32<TC>(u)), limit, slope, up_offset);
+                }
+                C[(size_t)(r0 + r) * ldc + n] = from_f32<TC>(g);
+            }
+        }
+    }
+}
+
 // Tensor-core form (bfloat16 operands, float32 accumulation): 64 sorted rows x 64 columns per block, four warps of
 // 16 rows each, `wmma` 16x16x16 fragments; A rows gathered through the row map into shared memory, W rows read in
 // place.  K % 16 == 0 and 16-byte aligned rows.
@@ -417,7 +585,29 @@ ZI_EXPORT int zi_moe_gemm(const void* A, int a_dtype, long long lda, const int* 
     if (n_rows <= 0 || N <= 0) return 0;
     if (K <= 0 || n_experts <= 0) return zi_fail("moe_gemm: K=%d experts=%d", K, n_experts);
     if (row_pair && pairs_per_src <= 0) return zi_fail("moe_gemm: pairs_per_src=%d", pairs_per_src);
-    const bool tc = allow_tensor_cores && a_dtype == ZI_BF16 && w_dtype == ZI_BF16 && c_dtype == ZI_BF16 && K % 8 == 0 &&
+    // few rows: the weight-streaming form (allow_tensor_cores & 2 switches it off)
+    if (n_rows <= 64 && !(allow_tensor_cores & 2) && (size_t)GV_ROWS * K * sizeof(float) <= 160 * 1024) {
+        const size_t smem = (size_t)GV_ROWS * K * sizeof(float);
+        dim3 grid((N + GV_WARPS - 1) / GV_WARPS, n_experts);
+        if (grid.y > 65535) return zi_fail("moe_gemm: %d experts are too many for one launch", n_experts);
+        ZI_DISPATCH(a_dtype, TA, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(c_dtype, TC, {
+            if (gated) {
+                auto fn = moe_gemv_kernel<TA, TW, TC, true>;
+                if (smem > 48 * 1024 && cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+                    return zi_fail("moe_gemm: cannot reserve %zu bytes of shared memory", smem);
+                fn<<<grid, GV_WARPS * 32, smem, stream>>>((const TA*)A, lda, row_pair, pairs_per_src, (const TW*)W, offsets, (TC*)C,
+                                                          ldc, N, K, limit, slope, up_offset);
+            } else {
+                auto fn = moe_gemv_kernel<TA, TW, TC, false>;
+                if (smem > 48 * 1024 && cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+                    return zi_fail("moe_gemm: cannot reserve %zu bytes of shared memory", smem);
+                fn<<<grid, GV_WARPS * 32, smem, stream>>>((const TA*)A, lda, row_pair, pairs_per_src, (const TW*)W, offsets, (TC*)C,
+                                                          ldc, N, K, limit, slope, up_offset);
+            }
+        });););
+        return zi_check_launch("moe_gemm");
+    }
+    const bool tc = (allow_tensor_cores & 1) && a_dtype == ZI_BF16 && w_dtype == ZI_BF16 && c_dtype == ZI_BF16 && K % 8 == 0 &&
                     lda % 8 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0;
     if (tc) {
         dim3 grid((N + TN_ - 1) / TN_, (n_rows + TM_ - 1) / TM_ + n_experts);
@@ -454,10 +644,42 @@ __global__ void moe_combine_kernel(const T* __restrict__ Y, const int* __restric
     }
 }
 
+// The same, eight columns per thread with 16- or 32-byte accesses (hidden % 8 == 0, aligned rows); the same sums.
+template <typename T>
+__global__ void moe_combine_vec8_kernel(const T* __restrict__ Y, const int* __restrict__ pair_row, const float* __restrict__ wts,
+                                        const T* __restrict__ shared, T* __restrict__ out, int top, int hidden) {
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x * 8; j < hidden; j += blockDim.x * 8) {
+        float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        for (int c = 0; c < top; ++c) {
+            const int r = pair_row[(size_t)t * top + c];
+            const float wt = wts[(size_t)t * top + c];
+            float v[8];
+            load8(Y + (size_t)r * hidden + j, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(wt, v[i], acc[i]);
+        }
+        if (shared) {
+            float v[8];
+            load8(shared + (size_t)t * hidden + j, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += v[i];
+        }
+        store8(out + (size_t)t * hidden + j, acc);
+    }
+}
+
 ZI_EXPORT int zi_moe_combine(const void* Y, const int* pair_row, const float* wts, const void* shared, void* out, int dtype,
                              int n_tokens, int top, int hidden, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top <= 0 || hidden <= 0) return zi_fail("moe_combine: top=%d hidden=%d", top, hidden);
+    if (hidden % 8 == 0 && (((uintptr_t)Y | (uintptr_t)shared | (uintptr_t)out) & 31) == 0) {
+        ZI_DISPATCH(dtype, T, {
+            moe_combine_vec8_kernel<T><<<n_tokens, hidden >= 2048 ? 256 : 128, 0, stream>>>((const T*)Y, pair_row, wts, (const T*)shared,
+                                                                                           (T*)out, top, hidden);
+        });
+        return zi_check_launch("moe_combine");
+    }
     ZI_DISPATCH(dtype, T, {
         moe_combine_kernel<T><<<n_tokens, hidden >= 1024 ? 256 : 128, 0, stream>>>((const T*)Y, pair_row, wts, (const T*)shared,
                                                                                   (T*)out, top, hidden);

@@ -34,7 +34,7 @@ __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", 
            "gemm_nt", "linear", "linear_for_residual", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode",
            "embedding_positions", "softcap", "relu2", "gated_clamp_mul", "rmsnorm_append", "linear_per_head", "route_topk",
            "moe_group", "moe_gemm", "moe_combine", "linear_gated_clamp_mul", "linear_relu2", "moe_group_padded",
-           "moe_gather_rows", "gemm_tcgen05_grouped"]
+           "moe_gather_rows", "gemm_tcgen05_grouped", "route"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -929,6 +929,23 @@ def route_topk(logits: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Ten
     _moe.call("zi_route_topk", ptr(logits), c_int(n), c_int(e), c_int(top), ptr(idx), ptr(wts), stream())
 
 
+def route(x: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor,
+          wts: torch.Tensor, logits: Optional[torch.Tensor] = None) -> None:
+    """The router in one kernel: float32 logits ``x @ w_router.T + bias`` (operands of any storage type, float32 sums in
+    a fixed order), then as :func:`route_topk`.  ``logits``: optional float32 ``[tokens, experts]`` to receive them."""
+    need_cuda(x, w_router, bias, idx, wts, logits)
+    need_int32("idx", idx)
+    need_contiguous("w_router", w_router), need_contiguous("idx", idx), need_contiguous("wts", wts)
+    n, k = x.shape
+    e = w_router.shape[0]
+    if (x.stride(1) != 1 or w_router.shape != (e, k) or idx.shape != (n, top) or wts.shape != (n, top) or wts.dtype != torch.float32
+            or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != e or not bias.is_contiguous()))
+            or (logits is not None and (logits.dtype != torch.float32 or logits.shape != (n, e) or not logits.is_contiguous()))):
+        raise KernelError(f"route: x {tuple(x.shape)}, w_router {tuple(w_router.shape)}, idx {tuple(idx.shape)}, wts {tuple(wts.shape)}")
+    _moe.call("zi_route", ptr(x), c_int(dtype_code(x.dtype)), c_ll(x.stride(0)), ptr(w_router), c_int(dtype_code(w_router.dtype)),
+              ptr(bias), c_int(n), c_int(k), c_int(e), c_int(top), ptr(idx), ptr(wts), ptr(logits), stream())
+
+
 def moe_group(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, row_pair: torch.Tensor, pair_row: torch.Tensor) -> None:
     """Group the (token, choice) pairs of ``idx`` (int32 ``[tokens, top]``) by expert: ``offsets`` (int32
     ``[experts + 1]``) bounds each expert's sorted rows, ``row_pair[r]`` is the pair at sorted row r and ``pair_row`` its
@@ -997,7 +1014,8 @@ def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Te
 
 
 MOE_TENSOR_CORES = True          # bfloat16 grouped products on the tensor cores (False: the SIMT form, as float32 uses)
-MOE_TCGEN05_MIN_PAIRS = 512      # from this many (token, choice) pairs the grouped products run on the tcgen05 kernel
+MOE_FEW_ROWS_STREAMING = True    # up to 64 sorted rows (decode steps) on the weight-streaming form of the grouped product
+MOE_TCGEN05_MIN_PAIRS = 65       # from this many (token, choice) pairs the grouped products run on the tcgen05 kernel
 
 
 def moe_gemm(a: torch.Tensor, row_pair: Optional[torch.Tensor], pairs_per_src: int, w: torch.Tensor, offsets: torch.Tensor,
@@ -1019,7 +1037,7 @@ def moe_gemm(a: torch.Tensor, row_pair: Optional[torch.Tensor], pairs_per_src: i
     _moe.call("zi_moe_gemm", ptr(a), c_int(dtype_code(a.dtype)), c_ll(a.stride(0)), ptr(row_pair), c_int(pairs_per_src), ptr(w),
               c_int(dtype_code(w.dtype)), ptr(offsets), c_int(e), ptr(out), c_int(dtype_code(out.dtype)), c_ll(out.stride(0)),
               c_int(rows), c_int(n), c_int(k), c_int(1 if gated else 0), c_float(limit), c_float(slope), c_float(up_offset),
-              c_int(1 if MOE_TENSOR_CORES else 0), stream())
+              c_int((1 if MOE_TENSOR_CORES else 0) | (0 if MOE_FEW_ROWS_STREAMING else 2)), stream())
 
 
 def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, wts: torch.Tensor, shared: Optional[torch.Tensor],

@@ -7,7 +7,7 @@ shared one that every token runs.
 
 Each expert has the form of :class:`~zedinfer_b200.parts.mlp.ClampedGatedMLP`.  Nothing goes to the host: the step's
 (token, choice) pairs are grouped by expert on the device, the two products run as grouped products over the sorted
-rows (``csrc/moe.cu``; the activation in the first one's epilogue), and one kernel adds a token's rows with its router
+rows (``csrc/moe.cu``, or the tcgen05 grouped product from a few hundred rows; the activation in the first one's epilogue), and one kernel adds a token's rows with its router
 weights and the shared expert's output in float32.
 """
 from __future__ import annotations
@@ -79,11 +79,9 @@ class RoutedExperts(FeedForward):
     def route(self, x: torch.Tensor):
         """(``idx`` int32 ``[tokens, top]``, ``wts`` float32 ``[tokens, top]``) of the step's tokens."""
         n = x.shape[0]
-        logits = torch.empty((n, self.experts), dtype=torch.float32, device=x.device)
-        ops.gemm_nt(x, self.w_router, self.b_router, logits)             # float32 sums and result whatever the operands
         idx = torch.empty((n, self.top), dtype=torch.int32, device=x.device)
         wts = torch.empty((n, self.top), dtype=torch.float32, device=x.device)
-        ops.route_topk(logits, self.top, idx, wts)
+        ops.route(x, self.w_router, self.b_router, self.top, idx, wts)    # float32 logits whatever the operands' type
         return idx, wts
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
