@@ -71,52 +71,82 @@ ZI_EXPORT int zi_route_topk(const float* logits, int n_tokens, int n_experts, in
 
 // ---------------------------------------------------------------------------------------
 // The router in one kernel: logits z[e] = x . Wr[e] + b[e] in float32 (x and Wr of any storage type), the `top`
-// largest and the softmax over them.  One block per token: the row of x waits in shared memory as float32, every
-// warp takes experts w, w + 4, ...; a lane's partial sum runs over k in rising order and the warp adds the lanes in a
-// fixed order, so a token's logits depend on nothing else in the step.  Then the first warp chooses as
+// largest and the softmax over them.  One block per four tokens: their rows of x wait in shared memory as float32, every
+// warp takes experts w, w + 4, ... for all four; a lane's partial sum runs over k in rising order and the warp adds the lanes in a
+// fixed order, so a token's logits depend on nothing else in the step.  Then warp r chooses for the block's token r as
 // route_topk_kernel does.
 // ---------------------------------------------------------------------------------------
 #define RF_WARPS 4
+#define RF_TOK 4                     // tokens per block (one per warp when it comes to choosing): a weight row is read once for all
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(RF_WARPS * 32)
 route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict__ w, const float* __restrict__ bias,
-                   int K, int n_experts, int top, int* __restrict__ idx, float* __restrict__ wts,
+                   int n_tokens, int K, int n_experts, int top, int* __restrict__ idx, float* __restrict__ wts,
                    float* __restrict__ logits_out) {
-    extern __shared__ float rf_smem[];              // x row [K], then logits [n_experts]
+    extern __shared__ __align__(16) float rf_smem[];              // x rows [RF_TOK][K], then logits [RF_TOK][n_experts]
     float* xs = rf_smem;
-    float* z = rf_smem + K;
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const TX* xr = x + (size_t)t * ldx;
-    for (int k = threadIdx.x; k < K; k += RF_WARPS * 32) xs[k] = to_f32<TX>(xr[k]);
+    float* z = rf_smem + RF_TOK * K;
+    const int t0 = blockIdx.x * RF_TOK, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int toks = n_tokens - t0 < RF_TOK ? n_tokens - t0 : RF_TOK;
+    if (K % 8 == 0 && ldx % 8 == 0 && (((uintptr_t)x) & 31) == 0) {
+        for (int i = threadIdx.x * 8; i < RF_TOK * K; i += RF_WARPS * 32 * 8) {
+            const int r = i / K, k = i - r * K;
+            float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            if (r < toks) load8(x + (size_t)(t0 + r) * ldx + k, v);
+            store8(xs + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < RF_TOK * K; i += RF_WARPS * 32) {
+            const int r = i / K, k = i - r * K;
+            xs[i] = r < toks ? to_f32<TX>(x[(size_t)(t0 + r) * ldx + k]) : 0.0f;
+        }
+    }
     __syncthreads();
     for (int e = warp; e < n_experts; e += RF_WARPS) {
         const TW* wr = w + (size_t)e * K;
-        float acc = 0.0f;
-        if (K % 8 == 0 && (((uintptr_t)wr) & (sizeof(TW) * 8 - 1)) == 0) {
+        float acc[RF_TOK];
+#pragma unroll
+        for (int r = 0; r < RF_TOK; ++r) acc[r] = 0.0f;
+        if (K % 8 == 0 && (((uintptr_t)wr) & 15) == 0) {
             for (int k = lane * 8; k < K; k += 256) {
                 float wv[8];
                 load8(wr + k, wv);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc = fmaf(xs[k + i], wv[i], acc);
+                for (int r = 0; r < RF_TOK; ++r) {
+                    const float4 x0 = *reinterpret_cast<const float4*>(xs + r * K + k);
+                    const float4 x1 = *reinterpret_cast<const float4*>(xs + r * K + k + 4);
+                    const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[r] = fmaf(xv[i], wv[i], acc[r]);
+                }
             }
         } else {
-            for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], to_f32<TW>(wr[k]), acc);
+            for (int k = lane; k < K; k += 32) {
+                const float wv = to_f32<TW>(wr[k]);
+#pragma unroll
+                for (int r = 0; r < RF_TOK; ++r) acc[r] = fmaf(xs[r * K + k], wv, acc[r]);
+            }
         }
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            const float v = acc + (bias ? bias[e] : 0.0f);
-            z[e] = v;
-            if (logits_out) logits_out[(size_t)t * n_experts + e] = v;
+#pragma unroll
+        for (int r = 0; r < RF_TOK; ++r) {
+            const float sum = warp_sum(acc[r]);
+            if (lane == 0 && r < toks) {
+                const float v = sum + (bias ? bias[e] : 0.0f);
+                z[r * n_experts + e] = v;
+                if (logits_out) logits_out[(size_t)(t0 + r) * n_experts + e] = v;
+            }
         }
     }
     __syncthreads();
-    if (warp != 0) return;
+    if (warp >= toks) return;                       // warp r chooses for token t0 + r
+    const int t = t0 + warp;
+    float* zt = z + warp * n_experts;
     float first = 0.0f, denom = 0.0f;
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
         int best_e = 0x7fffffff;
         for (int e = lane; e < n_experts; e += 32) {
-            const float v = z[e];
+            const float v = zt[e];
             if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
         }
 #pragma unroll
@@ -131,7 +161,7 @@ route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict
         if (lane == 0) {
             idx[(size_t)t * top + j] = best_e;
             wts[(size_t)t * top + j] = p;
-            z[best_e] = -INFINITY;
+            zt[best_e] = -INFINITY;
         }
         __syncwarp();
     }
@@ -145,7 +175,7 @@ ZI_EXPORT int zi_route(const void* x, int x_dtype, long long ldx, const void* w,
     if (n_tokens <= 0) return 0;
     if (K <= 0 || n_experts <= 0 || n_experts > 4096) return zi_fail("route: K=%d experts=%d", K, n_experts);
     if (top <= 0 || top > n_experts) return zi_fail("route: top=%d of %d experts", top, n_experts);
-    const size_t smem = ((size_t)K + n_experts) * sizeof(float);
+    const size_t smem = (size_t)RF_TOK * ((size_t)K + n_experts) * sizeof(float);
     if (smem > 200 * 1024) return zi_fail("route: a row of %d values and %d logits do not fit shared memory", K, n_experts);
     ZI_DISPATCH(x_dtype, TX, ZI_DISPATCH(w_dtype, TW, {
         auto fn = route_fused_kernel<TX, TW>;
@@ -153,7 +183,8 @@ ZI_EXPORT int zi_route(const void* x, int x_dtype, long long ldx, const void* w,
             cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return zi_fail("route: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         }
-        fn<<<n_tokens, RF_WARPS * 32, smem, stream>>>((const TX*)x, ldx, (const TW*)w, bias, K, n_experts, top, idx, wts, logits_out);
+        fn<<<(n_tokens + RF_TOK - 1) / RF_TOK, RF_WARPS * 32, smem, stream>>>((const TX*)x, ldx, (const TW*)w, bias, n_tokens, K, n_experts, top,
+                                                                            idx, wts, logits_out);
     }););
     return zi_check_launch("route");
 }
@@ -401,12 +432,14 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restr
 }
 
 // Few rows (decode steps): the product is bound by reading every used expert's weight once.  A block takes one
-// expert and eight output columns, a warp one column: it streams that column's weight row (and, gated, the up row
-// that pairs with it) with 16-byte loads, six or more in flight per lane, against up to GV_ROWS of the expert's rows of
-// A that wait in shared memory as float32; float32 FMAs, lanes added in a fixed order.  An expert with more rows
-// takes them GV_ROWS at a time (its weight rows then come from L2).  Experts without rows cost an empty block.
+// expert and 32 output columns, a warp four of them: it streams those columns' weight rows (and, gated, the up rows
+// that pair with them) with 16-byte loads, four or eight independent ones per lane and step, against up to GV_ROWS of
+// the expert's rows of A that wait in shared memory as float32; float32 FMAs, lanes added in a fixed order.  An
+// expert with more rows takes them GV_ROWS at a time (its weight rows then come from L2).  Experts without rows cost
+// an empty block.
 #define GV_ROWS 4
 #define GV_WARPS 8
+#define GV_COLS 4
 template <typename TA, typename TW, typename TC, bool GATED>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ row_pair, int pairs_per_src,
@@ -416,66 +449,93 @@ moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__
     const int e = blockIdx.y, lo = offsets[e], hi = offsets[e + 1];
     if (lo >= hi) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * GV_WARPS + warp;
-    const TW* wg = W + ((size_t)e * (GATED ? 2 * N : N) + (n < N ? n : 0)) * K;
-    const TW* wu = wg + (size_t)N * K;
+    const int n0 = (blockIdx.x * GV_WARPS + warp) * GV_COLS;
+    const TW* we = W + (size_t)e * (GATED ? 2 * N : N) * K;
+    const TW* wg[GV_COLS];
+#pragma unroll
+    for (int c = 0; c < GV_COLS; ++c) wg[c] = we + (size_t)(n0 + c < N ? n0 + c : 0) * K;      // columns beyond N: a valid row, never stored
+    const size_t up = (size_t)N * K;
     const bool vec = K % 8 == 0 && ((((uintptr_t)W) & 31) == 0);
+    const bool vec_a = K % 8 == 0 && lda % 8 == 0 && ((((uintptr_t)A) & 31) == 0);
     for (int r0 = lo; r0 < hi; r0 += GV_ROWS) {
         const int rows = hi - r0 < GV_ROWS ? hi - r0 : GV_ROWS;
         __syncthreads();
-        for (int i = threadIdx.x; i < GV_ROWS * K; i += GV_WARPS * 32) {
-            const int r = i / K, k = i - r * K;
-            float v = 0.0f;
-            if (r < rows) {
+        if (vec_a) {
+            for (int i = threadIdx.x * 8; i < rows * K; i += GV_WARPS * 32 * 8) {
+                const int r = i / K, k = i - r * K;
                 const int src = row_pair ? row_pair[r0 + r] / pairs_per_src : r0 + r;
-                v = to_f32<TA>(A[(size_t)src * lda + k]);
+                float v[8];
+                load8(A + (size_t)src * lda + k, v);
+                store8(gv_x + i, v);
             }
-            gv_x[i] = v;
+        } else {
+            for (int i = threadIdx.x; i < rows * K; i += GV_WARPS * 32) {
+                const int r = i / K, k = i - r * K;
+                const int src = row_pair ? row_pair[r0 + r] / pairs_per_src : r0 + r;
+                gv_x[i] = to_f32<TA>(A[(size_t)src * lda + k]);
+            }
         }
         __syncthreads();
-        if (n >= N) continue;
-        float ag[GV_ROWS], au[GV_ROWS];
+        if (n0 >= N) continue;
+        float ag[GV_COLS][GV_ROWS], au[GV_COLS][GV_ROWS];
 #pragma unroll
-        for (int r = 0; r < GV_ROWS; ++r) ag[r] = au[r] = 0.0f;
+        for (int c = 0; c < GV_COLS; ++c)
+#pragma unroll
+            for (int r = 0; r < GV_ROWS; ++r) ag[c][r] = au[c][r] = 0.0f;
         if (vec) {
+#pragma unroll 2
             for (int k = lane * 8; k < K; k += 256) {
-                float wv[8], uv[8];
-                load8(wg + k, wv);
-                if (GATED) load8(wu + k, uv);
+                float wv[GV_COLS][8], uv[GV_COLS][8];
+#pragma unroll
+                for (int c = 0; c < GV_COLS; ++c) {
+                    load8(wg[c] + k, wv[c]);
+                    if (GATED) load8(wg[c] + up + k, uv[c]);
+                }
 #pragma unroll
                 for (int r = 0; r < GV_ROWS; ++r) {
-                    const float4 x0 = *reinterpret_cast<const float4*>(gv_x + r * K + k);
-                    const float4 x1 = *reinterpret_cast<const float4*>(gv_x + r * K + k + 4);
-                    const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                    if (r < rows) {
+                        const float4 x0 = *reinterpret_cast<const float4*>(gv_x + r * K + k);
+                        const float4 x1 = *reinterpret_cast<const float4*>(gv_x + r * K + k + 4);
+                        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        ag[r] = fmaf(xv[i], wv[i], ag[r]);
-                        if (GATED) au[r] = fmaf(xv[i], uv[i], au[r]);
+                        for (int c = 0; c < GV_COLS; ++c)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                ag[c][r] = fmaf(xv[i], wv[c][i], ag[c][r]);
+                                if (GATED) au[c][r] = fmaf(xv[i], uv[c][i], au[c][r]);
+                            }
                     }
                 }
             }
         } else {
             for (int k = lane; k < K; k += 32) {
-                const float wv = to_f32<TW>(wg[k]), uv = GATED ? to_f32<TW>(wu[k]) : 0.0f;
 #pragma unroll
-                for (int r = 0; r < GV_ROWS; ++r) {
-                    ag[r] = fmaf(gv_x[r * K + k], wv, ag[r]);
-                    if (GATED) au[r] = fmaf(gv_x[r * K + k], uv, au[r]);
+                for (int c = 0; c < GV_COLS; ++c) {
+                    const float wv = to_f32<TW>(wg[c][k]), uv = GATED ? to_f32<TW>(wg[c][up + k]) : 0.0f;
+#pragma unroll
+                    for (int r = 0; r < GV_ROWS; ++r) {
+                        if (r < rows) {
+                            ag[c][r] = fmaf(gv_x[r * K + k], wv, ag[c][r]);
+                            if (GATED) au[c][r] = fmaf(gv_x[r * K + k], uv, au[c][r]);
+                        }
+                    }
                 }
             }
         }
 #pragma unroll
-        for (int r = 0; r < GV_ROWS; ++r) {
-            float g = warp_sum(ag[r]);
-            float u = GATED ? warp_sum(au[r]) : 0.0f;
-            if (lane == 0 && r < rows) {
-                if (GATED) {
-                    // the two halves are rounded to the storage type first, as a separate product would have stored them
-                    g = clamped_gate(to_f32<TC>(from_f32<TC>(g)), to_f32<TC>(from_f32<TC>(u)), limit, slope, up_offset);
+        for (int c = 0; c < GV_COLS; ++c)
+#pragma unroll
+            for (int r = 0; r < GV_ROWS; ++r) {
+                float g = warp_sum(ag[c][r]);
+                float u = GATED ? warp_sum(au[c][r]) : 0.0f;
+                if (lane == 0 && r < rows && n0 + c < N) {
+                    if (GATED) {
+                        // the two halves are rounded to the storage type first, as a separate product would have stored them
+                        g = clamped_gate(to_f32<TC>(from_f32<TC>(g)), to_f32<TC>(from_f32<TC>(u)), limit, slope, up_offset);
+                    }
+                    C[(size_t)(r0 + r) * ldc + n0 + c] = from_f32<TC>(g);
                 }
-                C[(size_t)(r0 + r) * ldc + n] = from_f32<TC>(g);
             }
-        }
     }
 }
 
@@ -588,7 +648,7 @@ ZI_EXPORT int zi_moe_gemm(const void* A, int a_dtype, long long lda, const int* 
     // few rows: the weight-streaming form (allow_tensor_cores & 2 switches it off)
     if (n_rows <= 64 && !(allow_tensor_cores & 2) && (size_t)GV_ROWS * K * sizeof(float) <= 160 * 1024) {
         const size_t smem = (size_t)GV_ROWS * K * sizeof(float);
-        dim3 grid((N + GV_WARPS - 1) / GV_WARPS, n_experts);
+        dim3 grid((N + GV_WARPS * GV_COLS - 1) / (GV_WARPS * GV_COLS), n_experts);
         if (grid.y > 65535) return zi_fail("moe_gemm: %d experts are too many for one launch", n_experts);
         ZI_DISPATCH(a_dtype, TA, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(c_dtype, TC, {
             if (gated) {
