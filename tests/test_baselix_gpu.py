@@ -289,7 +289,7 @@ def write_latents(view, tables, c):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rank,heads,window,page", [(64, 4, 21, 8), (128, 8, 40, 16), (32, 3, 7, 4), (320, 2, 33, 16),
+@pytest.mark.parametrize("rank,heads,window,page", [(64, 4, 21, 8), (128, 6, 37, 16), (32, 3, 7, 4), (320, 2, 33, 16),
                                                    (64, 20, 16, 16), (64, 5, 70, 24), (128, 2, 50, 12), (128, 17, 9, 128)])
 def test_attention_over_latents_sees_exactly_its_window_and_the_sink(dtype, rank, heads, window, page):
     """One score made to stand out: a query is aligned with the latent of one chosen key whose other coordinates carry a

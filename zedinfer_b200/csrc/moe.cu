@@ -71,14 +71,15 @@ ZI_EXPORT int zi_route_topk(const float* logits, int n_tokens, int n_experts, in
 
 // ---------------------------------------------------------------------------------------
 // The router in one kernel: logits z[e] = x . Wr[e] + b[e] in float32 (x and Wr of any storage type), the `top`
-// largest and the softmax over them.  One block per four tokens: their rows of x wait in shared memory as float32, every
-// warp takes experts w, w + 4, ... for all four; a lane's partial sum runs over k in rising order and the warp adds the lanes in a
+// largest and the softmax over them.  A block takes one or four tokens: their rows of x wait in shared memory as float32,
+// every warp takes experts w, w + 8, ... for all of them; a lane's partial sum runs over k in rising order and the warp adds the lanes in a
 // fixed order, so a token's logits depend on nothing else in the step.  Then warp r chooses for the block's token r as
 // route_topk_kernel does.
 // ---------------------------------------------------------------------------------------
-#define RF_WARPS 4
-#define RF_TOK 4                     // tokens per block (one per warp when it comes to choosing): a weight row is read once for all
-template <typename TX, typename TW>
+#define RF_WARPS 8
+// RF_TOK tokens per block (one per warp when it comes to choosing), so that a weight row is read once for all of them:
+// four for steps of many tokens, one for decode steps, whose few tokens want as many blocks as they can get.
+template <typename TX, typename TW, int RF_TOK>
 __global__ void __launch_bounds__(RF_WARPS * 32)
 route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict__ w, const float* __restrict__ bias,
                    int n_tokens, int K, int n_experts, int top, int* __restrict__ idx, float* __restrict__ wts,
@@ -175,16 +176,17 @@ ZI_EXPORT int zi_route(const void* x, int x_dtype, long long ldx, const void* w,
     if (n_tokens <= 0) return 0;
     if (K <= 0 || n_experts <= 0 || n_experts > 4096) return zi_fail("route: K=%d experts=%d", K, n_experts);
     if (top <= 0 || top > n_experts) return zi_fail("route: top=%d of %d experts", top, n_experts);
-    const size_t smem = (size_t)RF_TOK * ((size_t)K + n_experts) * sizeof(float);
+    const int tok = n_tokens > 64 ? 4 : 1;
+    const size_t smem = (size_t)tok * ((size_t)K + n_experts) * sizeof(float);
     if (smem > 200 * 1024) return zi_fail("route: a row of %d values and %d logits do not fit shared memory", K, n_experts);
     ZI_DISPATCH(x_dtype, TX, ZI_DISPATCH(w_dtype, TW, {
-        auto fn = route_fused_kernel<TX, TW>;
+        auto fn = tok == 4 ? route_fused_kernel<TX, TW, 4> : route_fused_kernel<TX, TW, 1>;
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return zi_fail("route: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         }
-        fn<<<(n_tokens + RF_TOK - 1) / RF_TOK, RF_WARPS * 32, smem, stream>>>((const TX*)x, ldx, (const TW*)w, bias, n_tokens, K, n_experts, top,
-                                                                            idx, wts, logits_out);
+        fn<<<(n_tokens + tok - 1) / tok, RF_WARPS * 32, smem, stream>>>((const TX*)x, ldx, (const TW*)w, bias, n_tokens, K, n_experts, top,
+                                                                        idx, wts, logits_out);
     }););
     return zi_check_launch("route");
 }
@@ -432,16 +434,18 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restr
 }
 
 // Few rows (decode steps): the product is bound by reading every used expert's weight once.  A block takes one
-// expert and 32 output columns, a warp four of them: it streams those columns' weight rows (and, gated, the up rows
+// expert and 32 (gated: 16) output columns, a warp four (two) of them: it streams those columns' weight rows (and, gated, the up rows
 // that pair with them) with 16-byte loads, four or eight independent ones per lane and step, against up to GV_ROWS of
 // the expert's rows of A that wait in shared memory as float32; float32 FMAs, lanes added in a fixed order.  An
 // expert with more rows takes them GV_ROWS at a time (its weight rows then come from L2).  Experts without rows cost
 // an empty block.
 #define GV_ROWS 4
 #define GV_WARPS 8
-#define GV_COLS 4
+// columns per warp: four, or two with the gate (twice the sums and weights per column); either way at most 128
+// registers, so that two blocks share an SM and one's start and end overlap with the other's streaming
+#define GV_COLS (GATED ? 2 : 4)
 template <typename TA, typename TW, typename TC, bool GATED>
-__global__ void __launch_bounds__(GV_WARPS * 32)
+__global__ void __launch_bounds__(GV_WARPS * 32, 2)
 moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ row_pair, int pairs_per_src,
                 const TW* __restrict__ W, const int* __restrict__ offsets, TC* __restrict__ C, long long ldc, int N, int K,
                 float limit, float slope, float up_offset) {
@@ -648,7 +652,8 @@ ZI_EXPORT int zi_moe_gemm(const void* A, int a_dtype, long long lda, const int* 
     // few rows: the weight-streaming form (allow_tensor_cores & 2 switches it off)
     if (n_rows <= 64 && !(allow_tensor_cores & 2) && (size_t)GV_ROWS * K * sizeof(float) <= 160 * 1024) {
         const size_t smem = (size_t)GV_ROWS * K * sizeof(float);
-        dim3 grid((N + GV_WARPS * GV_COLS - 1) / (GV_WARPS * GV_COLS), n_experts);
+        const int cols = GV_WARPS * (gated ? 2 : 4);              // GV_COLS of the kernel that runs
+        dim3 grid((N + cols - 1) / cols, n_experts);
         if (grid.y > 65535) return zi_fail("moe_gemm: %d experts are too many for one launch", n_experts);
         ZI_DISPATCH(a_dtype, TA, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(c_dtype, TC, {
             if (gated) {
