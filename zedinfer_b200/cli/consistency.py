@@ -106,11 +106,17 @@ def main(argv=None) -> int:
     if args.tokens < 48:
         print("--tokens must be at least 48", file=sys.stderr)
         return 1
+    from ..config.registry import resolve_architecture
     raw = read_config_json(args.model_path)
     if args.layers is not None:
-        raw = dict(raw, num_hidden_layers=args.layers)
+        # an architecture counts its layers under a key, or lists them one by one
+        if isinstance(raw.get("layers"), list):
+            raw = dict(raw, layers=raw["layers"][:args.layers])
+        else:
+            raw = dict(raw, num_hidden_layers=args.layers)
     rng = random.Random(args.seed)
-    vocab = raw["vocab_size"]
+    arch = resolve_architecture(raw)
+    vocab = arch.build_spec(arch.parse(raw)).vocab_size
     lengths = [args.tokens] + [rng.randrange(40, args.tokens + 1) for _ in range(args.requests - 1)]
     requests = {f"r{i}": [rng.randrange(vocab) for _ in range(n)] for i, n in enumerate(lengths)}
     page = args.kv_block_size

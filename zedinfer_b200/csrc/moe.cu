@@ -650,7 +650,10 @@ ZI_EXPORT int zi_moe_gemm(const void* A, int a_dtype, long long lda, const int* 
     if (K <= 0 || n_experts <= 0) return zi_fail("moe_gemm: K=%d experts=%d", K, n_experts);
     if (row_pair && pairs_per_src <= 0) return zi_fail("moe_gemm: pairs_per_src=%d", pairs_per_src);
     // few rows: the weight-streaming form (allow_tensor_cores & 2 switches it off)
-    if (n_rows <= 64 && !(allow_tensor_cores & 2) && (size_t)GV_ROWS * K * sizeof(float) <= 160 * 1024) {
+    // ... and so does a product all in float32: the SIMT form below adds every output's terms in rising k whatever the
+    // number of rows, so float32 results do not depend on how a step was cut
+    const bool all_f32 = a_dtype == ZI_F32 && w_dtype == ZI_F32 && c_dtype == ZI_F32;
+    if (n_rows <= 64 && !(allow_tensor_cores & 2) && !all_f32 && (size_t)GV_ROWS * K * sizeof(float) <= 160 * 1024) {
         const size_t smem = (size_t)GV_ROWS * K * sizeof(float);
         const int cols = GV_WARPS * (gated ? 2 : 4);              // GV_COLS of the kernel that runs
         dim3 grid((N + cols - 1) / cols, n_experts);
