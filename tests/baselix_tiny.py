@@ -2,7 +2,7 @@
 value sizes that differ from each other, latent ranks (32: the general attention kernel; 64 and 128: the tensor-core
 kernels; 320: beyond 256), windows that are no multiple of a page, a borrower whose window is wider than its owner's,
 layers without a feed-forward, routed layers with and without a shared expert, top 1 and top = experts, a residual
-factor of 1 and others, with and without a logit cap."""
+factor of 1 and others, with and without a logit cap, and one (E) whose sizes fit no vector width."""
 import os
 
 
@@ -56,7 +56,17 @@ BX_D = {
         _layer(_mixer(1, 40, 48, 320, 19, 0.15, kv_from=0), _moe(32, 1.0, 4, 2, {"ff": 24, "limit": 1.0})),
     ],
 }
-CONFIGS = {"A": (BX_A, 21), "B": (BX_B, 22), "C": (BX_C, 23), "D": (BX_D, 24)}
+# sizes that fit no vector width: a width that is no multiple of 8, 5 heads of 12, values of 20, rank 40, 7 experts
+BX_E = {
+    "architecture": "Baselix", "vocab": 203, "width": 100, "max_positions": 300, "norm": {"eps": 1e-5},
+    "residual_mult": 0.6, "logit_softcap": 8.0,
+    "layers": [
+        _layer(_mixer(5, 12, 20, 40, 13, 0.3), _moe(36, 1.2, 7, 3, {"ff": 52, "limit": 0.9})),
+        _layer(_mixer(5, 12, 20, 40, 26, 0.3, kv_from=0), {"kind": "dense", "ff": 90}),
+        _layer(_mixer(3, 20, 12, 24, 8, 0.25), _moe(44, 2.0, 2, 1)),
+    ],
+}
+CONFIGS = {"A": (BX_A, 21), "B": (BX_B, 22), "C": (BX_C, 23), "D": (BX_D, 24), "E": (BX_E, 25)}
 INIT_SCALE = 5.0
 
 

@@ -418,12 +418,12 @@ def judge(got, exp, dtype):
     assert all(e == e and e < 1e30 for e in errs.values())
 
 
-LENGTHS = {"A": [7, 13, 95, 45], "B": [1, 17, 120, 64], "C": [150, 5, 80], "D": [50, 2, 61]}
-PAGES = {"A": 4, "B": 16, "C": 16, "D": 8}
+LENGTHS = {"A": [7, 13, 95, 45], "B": [1, 17, 120, 64], "C": [150, 5, 80], "D": [50, 2, 61], "E": [66, 3, 140]}
+PAGES = {"A": 4, "B": 16, "C": 16, "D": 8, "E": 16}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("family", ["whole", "tail", "chunks", "mixed"])
 def test_cuts_match_plain(models, name, dtype, family):
     """Whole prompts; a tail decoded token by token (longer than every window); portions down to two tokens; mixed
