@@ -444,21 +444,23 @@ def test_cuts_match_plain(models, name, dtype, family):
 
 
 @pytest.mark.parametrize("graphs", [False, True])
-@pytest.mark.parametrize("name", ["A", "B"])
-def test_many_decoding_requests_with_and_without_graphs(models, name, graphs):
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("B", "bfloat16"), ("C", "bfloat16")])
+def test_many_decoding_requests_with_and_without_graphs(models, name, dtype, graphs):
     """Steps as a scheduler makes them: up to 12 decoding requests beside one prompt portion, then decode-only steps whose
-    number of rows falls to one; with graphs the decode-only steps replay captured buckets."""
+    number of rows falls to one; with graphs the decode-only steps replay captured buckets (bfloat16 with ranks 64 and 128:
+    the TMA decode kernel and the tcgen05 prefill kernel with sinks inside captured steps)."""
     from zedinfer_b200.engine.core import EngineCore
     cfg, _ = BT.CONFIGS[name]
     rng = random.Random(8)
     requests = make_requests(cfg, [rng.randint(40, 90) for _ in range(15)], seed=3)
     steps = traces.decode_heavy(requests, seed=4, max_live=12, tail=(8, 30), portion=32)
     need = traces.max_live_tokens(steps, round_to=16)
-    core = EngineCore(models[name], "float32", page_size=16, num_pages=need // 16, max_requests=16, cuda_graphs=graphs)
+    core = EngineCore(models[name], dtype, page_size=16, num_pages=need // 16, max_requests=16, cuda_graphs=graphs)
     core.GPU_BOUND_RATIO = float("inf")
     assert core.capture_safe, core.capture_blockers
     got = run_trace(core, steps)
-    judge(got, expected_logits(models[name], requests), "float32")
+    core.check_kernels()
+    judge(got, expected_logits(models[name], requests), dtype)
     if graphs:
         assert core._decode_graphs
     assert core.cache.num_live == 0 and all(g.pool.num_used == 0 for g in core.cache.groups)
