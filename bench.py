@@ -311,7 +311,7 @@ def baselix_config(width, heads, ff, window, layers, vocab, experts, top, expert
                         "mlp": {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
                                 "router": {"experts": experts, "top": top}, "shared": {"ff": shared_ff, "limit": 7.0}}})
     return {"architecture": "Baselix", "vocab": vocab, "width": width, "max_positions": CONTEXT, "norm": {"eps": 1e-6},
-            "residual_mult": 0.5, "logit_softcap": 30.0, "layers": out}
+            "residual_mult": 0.5, "logit_softcap": 50.0, "layers": out}
 
 
 def qwen2_config_like(width, heads, ff, window, layers, vocab, dim=128):
