@@ -89,17 +89,22 @@ route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict
     float* z = rf_smem + RF_TOK * K;
     const int t0 = blockIdx.x * RF_TOK, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int toks = n_tokens - t0 < RF_TOK ? n_tokens - t0 : RF_TOK;
-    if (K % 8 == 0 && ldx % 8 == 0 && (((uintptr_t)x) & 31) == 0) {
+    // Rows that are read eight values per lane (vec) lie in two halves: values 8c .. 8c+3 of chunk c at 4c, values
+    // 8c+4 .. 8c+7 at K/2 + 4c, so that the lanes of a warp read consecutive 16 bytes and meet no bank twice.
+    const bool vec = K % 8 == 0 && (((uintptr_t)w) & 15) == 0;
+    if (vec && ldx % 8 == 0 && (((uintptr_t)x) & 31) == 0) {
         for (int i = threadIdx.x * 8; i < RF_TOK * K; i += RF_WARPS * 32 * 8) {
             const int r = i / K, k = i - r * K;
             float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
             if (r < toks) load8(x + (size_t)(t0 + r) * ldx + k, v);
-            store8(xs + i, v);
+            *reinterpret_cast<float4*>(xs + r * K + (k >> 1)) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(xs + r * K + (K >> 1) + (k >> 1)) = make_float4(v[4], v[5], v[6], v[7]);
         }
     } else {
         for (int i = threadIdx.x; i < RF_TOK * K; i += RF_WARPS * 32) {
             const int r = i / K, k = i - r * K;
-            xs[i] = r < toks ? to_f32<TX>(x[(size_t)(t0 + r) * ldx + k]) : 0.0f;
+            const int at = vec ? ((k & 7) < 4 ? ((k >> 3) << 2) + (k & 3) : (K >> 1) + ((k >> 3) << 2) + (k & 3)) : k;
+            xs[r * K + at] = r < toks ? to_f32<TX>(x[(size_t)(t0 + r) * ldx + k]) : 0.0f;
         }
     }
     __syncthreads();
@@ -108,14 +113,14 @@ route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict
         float acc[RF_TOK];
 #pragma unroll
         for (int r = 0; r < RF_TOK; ++r) acc[r] = 0.0f;
-        if (K % 8 == 0 && (((uintptr_t)wr) & 15) == 0) {
+        if (vec) {
             for (int k = lane * 8; k < K; k += 256) {
                 float wv[8];
                 load8(wr + k, wv);
 #pragma unroll
                 for (int r = 0; r < RF_TOK; ++r) {
-                    const float4 x0 = *reinterpret_cast<const float4*>(xs + r * K + k);
-                    const float4 x1 = *reinterpret_cast<const float4*>(xs + r * K + k + 4);
+                    const float4 x0 = *reinterpret_cast<const float4*>(xs + r * K + (k >> 1));
+                    const float4 x1 = *reinterpret_cast<const float4*>(xs + r * K + (K >> 1) + (k >> 1));
                     const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
                     for (int i = 0; i < 8; ++i) acc[r] = fmaf(xv[i], wv[i], acc[r]);
@@ -464,19 +469,22 @@ moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__
     for (int r0 = lo; r0 < hi; r0 += GV_ROWS) {
         const int rows = hi - r0 < GV_ROWS ? hi - r0 : GV_ROWS;
         __syncthreads();
-        if (vec_a) {
+        // rows that are read eight values per lane (vec) lie in two halves, as in route_fused_kernel
+        if (vec && vec_a) {
             for (int i = threadIdx.x * 8; i < rows * K; i += GV_WARPS * 32 * 8) {
                 const int r = i / K, k = i - r * K;
                 const int src = row_pair ? row_pair[r0 + r] / pairs_per_src : r0 + r;
                 float v[8];
                 load8(A + (size_t)src * lda + k, v);
-                store8(gv_x + i, v);
+                *reinterpret_cast<float4*>(gv_x + r * K + (k >> 1)) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(gv_x + r * K + (K >> 1) + (k >> 1)) = make_float4(v[4], v[5], v[6], v[7]);
             }
         } else {
             for (int i = threadIdx.x; i < rows * K; i += GV_WARPS * 32) {
                 const int r = i / K, k = i - r * K;
                 const int src = row_pair ? row_pair[r0 + r] / pairs_per_src : r0 + r;
-                gv_x[i] = to_f32<TA>(A[(size_t)src * lda + k]);
+                const int at = vec ? ((k & 7) < 4 ? ((k >> 3) << 2) + (k & 3) : (K >> 1) + ((k >> 3) << 2) + (k & 3)) : k;
+                gv_x[r * K + at] = to_f32<TA>(A[(size_t)src * lda + k]);
             }
         }
         __syncthreads();
@@ -498,8 +506,8 @@ moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__
 #pragma unroll
                 for (int r = 0; r < GV_ROWS; ++r) {
                     if (r < rows) {
-                        const float4 x0 = *reinterpret_cast<const float4*>(gv_x + r * K + k);
-                        const float4 x1 = *reinterpret_cast<const float4*>(gv_x + r * K + k + 4);
+                        const float4 x0 = *reinterpret_cast<const float4*>(gv_x + r * K + (k >> 1));
+                        const float4 x1 = *reinterpret_cast<const float4*>(gv_x + r * K + (K >> 1) + (k >> 1));
                         const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
                         for (int c = 0; c < GV_COLS; ++c)
