@@ -72,11 +72,15 @@ class LayerCall:
 
     ``layer`` indexes :attr:`ModelSpec.layers`.  ``cache_of`` is ``None`` when the
     call owns a cache of its own, else the index (into the schedule) of an earlier
-    call whose cache this call reads without writing to it.
+    call whose cache this call reads without writing to it.  ``add_embedding``: the
+    embedding's output (the residual stream as it was before the first call) is added
+    to the residual stream, in float32, right before this call (a model that runs a
+    stretch of layers several times and feeds its input in again before each pass).
     """
 
     layer: int
     cache_of: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

@@ -44,6 +44,7 @@ SOURCES: Dict[str, str] = {
     "attention_tcgen05": "attention_tcgen05.cu",
     "rowwise": "rowwise.cu",
     "moe": "moe.cu",
+    "ssm": "ssm.cu",
 }
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 EXTRA_LIBS: Dict[str, List[str]] = {}

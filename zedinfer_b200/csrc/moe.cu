@@ -21,7 +21,7 @@ ZI_DEFINE_LAST_ERROR(moe)
 #define RT_MAX_PER_LANE 32            // experts <= 1024
 __global__ void __launch_bounds__(RT_WARPS * 32)
 route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int* __restrict__ idx,
-                  float* __restrict__ wts) {
+                  float* __restrict__ wts, int score) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * RT_WARPS + warp;
     if (t >= n_tokens) return;
@@ -48,7 +48,7 @@ route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts,
             if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
         }
         if (j == 0) first = best;                       // the largest of all: the softmax's reference point
-        const float p = expf(best - first);
+        const float p = score == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
         denom += p;
         if (lane == 0) { idx[(size_t)t * top + j] = best_e; wts[(size_t)t * top + j] = p; }
 #pragma unroll
@@ -56,16 +56,18 @@ route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts,
             if (lane + 32 * i == best_e) v[i] = -INFINITY;
     }
     __syncwarp();
-    if (lane == 0)
+    if (lane == 0 && score == 0)
         for (int j = 0; j < top; ++j) wts[(size_t)t * top + j] = wts[(size_t)t * top + j] / denom;
 }
 
-ZI_EXPORT int zi_route_topk(const float* logits, int n_tokens, int n_experts, int top, int* idx, float* wts,
+// score 0: the weights are the softmax over the chosen logits; 1: each chosen expert's own sigmoid(logit), not renormalised
+ZI_EXPORT int zi_route_topk(const float* logits, int n_tokens, int n_experts, int top, int* idx, float* wts, int score,
                             cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_experts <= 0 || n_experts > 32 * RT_MAX_PER_LANE) return zi_fail("route_topk: %d experts (1..%d)", n_experts, 32 * RT_MAX_PER_LANE);
     if (top <= 0 || top > n_experts) return zi_fail("route_topk: top=%d of %d experts", top, n_experts);
-    route_topk_kernel<<<(n_tokens + RT_WARPS - 1) / RT_WARPS, RT_WARPS * 32, 0, stream>>>(logits, n_tokens, n_experts, top, idx, wts);
+    if (score < 0 || score > 1) return zi_fail("route_topk: unknown score rule %d", score);
+    route_topk_kernel<<<(n_tokens + RT_WARPS - 1) / RT_WARPS, RT_WARPS * 32, 0, stream>>>(logits, n_tokens, n_experts, top, idx, wts, score);
     return zi_check_launch("route_topk");
 }
 
@@ -83,7 +85,7 @@ template <typename TX, typename TW, int RF_TOK>
 __global__ void __launch_bounds__(RF_WARPS * 32)
 route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict__ w, const float* __restrict__ bias,
                    int n_tokens, int K, int n_experts, int top, int* __restrict__ idx, float* __restrict__ wts,
-                   float* __restrict__ logits_out) {
+                   float* __restrict__ logits_out, int score) {
     extern __shared__ __align__(16) float rf_smem[];              // x rows [RF_TOK][K], then logits [RF_TOK][n_experts]
     float* xs = rf_smem;
     float* z = rf_smem + RF_TOK * K;
@@ -162,7 +164,7 @@ route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict
             if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
         }
         if (j == 0) first = best;
-        const float p = expf(best - first);
+        const float p = score == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
         denom += p;
         if (lane == 0) {
             idx[(size_t)t * top + j] = best_e;
@@ -171,14 +173,15 @@ route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict
         }
         __syncwarp();
     }
-    if (lane == 0)
+    if (lane == 0 && score == 0)
         for (int j = 0; j < top; ++j) wts[(size_t)t * top + j] = wts[(size_t)t * top + j] / denom;
 }
 
-// logits_out: optional float32 [n_tokens, n_experts] (tests).  bias: float32 or null.
+// logits_out: optional float32 [n_tokens, n_experts] (tests).  bias: float32 or null.  score: as zi_route_topk.
 ZI_EXPORT int zi_route(const void* x, int x_dtype, long long ldx, const void* w, int w_dtype, const float* bias, int n_tokens,
-                       int K, int n_experts, int top, int* idx, float* wts, float* logits_out, cudaStream_t stream) {
+                       int K, int n_experts, int top, int* idx, float* wts, float* logits_out, int score, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (score < 0 || score > 1) return zi_fail("route: unknown score rule %d", score);
     if (K <= 0 || n_experts <= 0 || n_experts > 4096) return zi_fail("route: K=%d experts=%d", K, n_experts);
     if (top <= 0 || top > n_experts) return zi_fail("route: top=%d of %d experts", top, n_experts);
     const int tok = n_tokens > 64 ? 4 : 1;
@@ -191,7 +194,7 @@ ZI_EXPORT int zi_route(const void* x, int x_dtype, long long ldx, const void* w,
             if (e != cudaSuccess) return zi_fail("route: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         }
         fn<<<(n_tokens + tok - 1) / tok, RF_WARPS * 32, smem, stream>>>((const TX*)x, ldx, (const TW*)w, bias, n_tokens, K, n_experts, top,
-                                                                        idx, wts, logits_out);
+                                                                        idx, wts, logits_out, score);
     }););
     return zi_check_launch("route");
 }
@@ -282,29 +285,39 @@ ZI_EXPORT int zi_moe_group_padded(const int* idx, int n_pairs, int n_experts, in
     return zi_check_launch("moe_group_padded");
 }
 
-// Rows of x brought into sorted order: out[r, :] = x[row_pair[r] / pairs_per_src, :], zeros for a row of padding.
+// Rows of x brought into sorted order: out[r, :] = x[row_pair[r] / pairs_per_src, :] (times scale[row_pair[r]] where a
+// scale per pair is given, rounded once), zeros for a row of padding.
 // bfloat16, K % 8 == 0, 16-byte aligned rows.
 __global__ void moe_gather_rows_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ row_pair,
-                                       int pairs_per_src, bf16* __restrict__ out, int n_rows, int k8) {
+                                       int pairs_per_src, bf16* __restrict__ out, int n_rows, int k8,
+                                       const float* __restrict__ scale) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)n_rows * k8;
          i += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(i / k8), c = (int)(i - (long long)r * k8);
         const int pair = row_pair[r];
         uint4 v = make_uint4(0, 0, 0, 0);
         if (pair >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)(pair / pairs_per_src) * ldx + c * 8);
+        if (scale && pair >= 0) {
+            float f[8];
+            load8(reinterpret_cast<const bf16*>(&v), f);
+            const float sc = scale[pair];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) f[q] *= sc;
+            store8(reinterpret_cast<bf16*>(&v), f);
+        }
         *reinterpret_cast<uint4*>(out + (size_t)r * k8 * 8 + c * 8) = v;
     }
 }
 
 ZI_EXPORT int zi_moe_gather_rows(const void* x, long long ldx, const int* row_pair, int pairs_per_src, void* out, int n_rows,
-                                 int K, cudaStream_t stream) {
+                                 int K, const float* scale, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || (((uintptr_t)x | (uintptr_t)out) & 15) || pairs_per_src <= 0)
         return zi_fail("moe_gather_rows: K=%d and the rows must be multiples of 8 elements and 16-byte aligned", K);
     const long long total = (long long)n_rows * (K / 8);
     const long long want = (total + 255) / 256;
     moe_gather_rows_kernel<<<(int)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>((const bf16*)x, ldx, row_pair, pairs_per_src,
-                                                                                       (bf16*)out, n_rows, K / 8);
+                                                                                       (bf16*)out, n_rows, K / 8, scale);
     return zi_check_launch("moe_gather_rows");
 }
 
@@ -314,6 +327,9 @@ ZI_EXPORT int zi_moe_gather_rows(const void* x, long long ldx, const int* row_pa
 //   gated == 0: C[r, n] = A[src] . W[e, n]                                  (N_w = N)
 //   gated == 1: W holds gate rows then up rows (N_w = 2 N);
 //               C[r, n] = act(A[src] . W[e, n], A[src] . W[e, N + n])       (see clamped_gate)
+//   gated == 2: C[r, n] = max(A[src] . W[e, n], 0)^2                        (N_w = N)
+// a_scale (optional, float32, one per pair): the A row of sorted row r is multiplied by a_scale[row_pair[r]] (row_pair
+// null: a_scale[r]) and rounded to A's storage type before the product: a router weight on an expert's input.
 // Block b walks the experts' tiles of TM rows: the block's (expert, first row) is found from the offsets.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ float clamped_gate(float g, float u, float limit, float slope, float up_offset) {
@@ -350,11 +366,15 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 moe_gemm_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ row_pair, int pairs_per_src,
                      const TW* __restrict__ W, const int* __restrict__ offsets, int n_experts, TC* __restrict__ C,
-                     long long ldc, int N, int K, int gated, float limit, float slope, float up_offset) {
+                     long long ldc, int N, int K, int gated, float limit, float slope, float up_offset,
+                     const float* __restrict__ a_scale) {
     __shared__ float As[GK][GM + 1];
     __shared__ float Ws[2][GK][GN + 1];
     __shared__ int src_rows[GM];
+    __shared__ float src_scale[GM];
     __shared__ int tile_info[3];
+    const bool relu2 = gated == 2;
+    gated = gated == 1;
     if (threadIdx.x == 0) {
         int e = 0, r0 = 0, rend = 0;
         if (!find_tile(offsets, n_experts, blockIdx.y, GM, &e, &r0, &rend)) e = -1;
@@ -367,6 +387,7 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restr
     if (tid < GM) {
         const int r = r0 + tid;
         src_rows[tid] = r < rend ? (row_pair ? row_pair[r] / pairs_per_src : r) : -1;
+        src_scale[tid] = (a_scale && r < rend) ? a_scale[row_pair ? row_pair[r] : r] : 1.0f;
     }
     __syncthreads();
     const int n0 = blockIdx.x * GN;
@@ -386,7 +407,9 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restr
         for (int q = 0; q < 2; ++q) {
             const int i = tid * 2 + q, r = i / GK, k = k0 + i % GK;
             const int src = src_rows[r];
-            As[i % GK][r] = (src >= 0 && k < K) ? to_f32<TA>(A[(size_t)src * lda + k]) : 0.0f;
+            float av = (src >= 0 && k < K) ? to_f32<TA>(A[(size_t)src * lda + k]) : 0.0f;
+            if (a_scale) av = to_f32<TA>(from_f32<TA>(src_scale[r] * av));
+            As[i % GK][r] = av;
         }
         // W tile(s): 64 rows x 16 k = 1024 values, four per thread
 #pragma unroll
@@ -432,6 +455,9 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restr
                 // the two halves are rounded to the storage type first, as a separate product would have stored them
                 const float g = to_f32<TC>(from_f32<TC>(v)), u = to_f32<TC>(from_f32<TC>(acc[1][i][j]));
                 v = clamped_gate(g, u, limit, slope, up_offset);
+            } else if (relu2) {
+                v = fmaxf(to_f32<TC>(from_f32<TC>(v)), 0.0f);
+                v = v * v;
             }
             C[(size_t)r * ldc + n] = from_f32<TC>(v);
         }
@@ -453,7 +479,7 @@ template <typename TA, typename TW, typename TC, bool GATED>
 __global__ void __launch_bounds__(GV_WARPS * 32, 2)
 moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ row_pair, int pairs_per_src,
                 const TW* __restrict__ W, const int* __restrict__ offsets, TC* __restrict__ C, long long ldc, int N, int K,
-                float limit, float slope, float up_offset) {
+                float limit, float slope, float up_offset, const float* __restrict__ a_scale, int relu2) {
     extern __shared__ __align__(16) float gv_x[];                 // [GV_ROWS][K]
     const int e = blockIdx.y, lo = offsets[e], hi = offsets[e + 1];
     if (lo >= hi) return;
@@ -476,6 +502,11 @@ moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__
                 const int src = row_pair ? row_pair[r0 + r] / pairs_per_src : r0 + r;
                 float v[8];
                 load8(A + (size_t)src * lda + k, v);
+                if (a_scale) {
+                    const float sc = a_scale[row_pair ? row_pair[r0 + r] : r0 + r];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) v[q] = to_f32<TA>(from_f32<TA>(sc * v[q]));
+                }
                 *reinterpret_cast<float4*>(gv_x + r * K + (k >> 1)) = make_float4(v[0], v[1], v[2], v[3]);
                 *reinterpret_cast<float4*>(gv_x + r * K + (K >> 1) + (k >> 1)) = make_float4(v[4], v[5], v[6], v[7]);
             }
@@ -484,7 +515,9 @@ moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__
                 const int r = i / K, k = i - r * K;
                 const int src = row_pair ? row_pair[r0 + r] / pairs_per_src : r0 + r;
                 const int at = vec ? ((k & 7) < 4 ? ((k >> 3) << 2) + (k & 3) : (K >> 1) + ((k >> 3) << 2) + (k & 3)) : k;
-                gv_x[r * K + at] = to_f32<TA>(A[(size_t)src * lda + k]);
+                float av = to_f32<TA>(A[(size_t)src * lda + k]);
+                if (a_scale) av = to_f32<TA>(from_f32<TA>(a_scale[row_pair ? row_pair[r0 + r] : r0 + r] * av));
+                gv_x[r * K + at] = av;
             }
         }
         __syncthreads();
@@ -544,6 +577,9 @@ moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__
                     if (GATED) {
                         // the two halves are rounded to the storage type first, as a separate product would have stored them
                         g = clamped_gate(to_f32<TC>(from_f32<TC>(g)), to_f32<TC>(from_f32<TC>(u)), limit, slope, up_offset);
+                    } else if (relu2) {
+                        g = fmaxf(to_f32<TC>(from_f32<TC>(g)), 0.0f);
+                        g = g * g;
                     }
                     C[(size_t)(r0 + r) * ldc + n0 + c] = from_f32<TC>(g);
                 }
@@ -560,8 +596,12 @@ moe_gemv_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ row_pair, int pairs_per_src,
                     const bf16* __restrict__ W, const int* __restrict__ offsets, int n_experts, bf16* C,
-                    long long ldc, int N, int K, int gated, float limit, float slope, float up_offset) {
+                    long long ldc, int N, int K, int gated, float limit, float slope, float up_offset,
+                    const float* __restrict__ a_scale) {
     using namespace nvcuda;
+    const bool relu2 = gated == 2;
+    gated = gated == 1;
+    __shared__ float src_scale[TM_];
     __shared__ __align__(32) bf16 As[TM_][TK_ + 8];
     __shared__ __align__(32) bf16 Ws[2][TN_][TK_ + 8];
     __shared__ __align__(32) float Cs[4][16][TN_ + 4];
@@ -579,6 +619,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
     if (tid < TM_) {
         const int r = r0 + tid;
         src_rows[tid] = r < rend ? (row_pair ? row_pair[r] / pairs_per_src : r) : -1;
+        src_scale[tid] = (a_scale && r < rend) ? a_scale[row_pair ? row_pair[r] : r] : 1.0f;
     }
     __syncthreads();
     const int n0 = blockIdx.x * TN_;
@@ -596,8 +637,16 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
         for (int q = 0; q < 2; ++q) {
             const int i = tid * 2 + q, r = i >> 2, kc = (i & 3) * 8, k = k0 + kc;
             const int src = src_rows[r];
-            *reinterpret_cast<uint4*>(&As[r][kc]) =
-                (src >= 0 && k < K) ? *reinterpret_cast<const uint4*>(A + (size_t)src * lda + k) : zero;
+            if (a_scale && src >= 0 && k < K) {
+                float av[8];
+                load8(A + (size_t)src * lda + k, av);
+#pragma unroll
+                for (int t = 0; t < 8; ++t) av[t] *= src_scale[r];
+                store8(&As[r][kc], av);
+            } else {
+                *reinterpret_cast<uint4*>(&As[r][kc]) =
+                    (src >= 0 && k < K) ? *reinterpret_cast<const uint4*>(A + (size_t)src * lda + k) : zero;
+            }
             const int n = n0 + r;
             const bool ok = n < N && k < K;
             *reinterpret_cast<uint4*>(&Ws[0][r][kc]) = ok ? *reinterpret_cast<const uint4*>(We + (size_t)n * K + k) : zero;
@@ -641,6 +690,9 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
                 if (h == 0 && gated) {
                     const float g = to_f32<bf16>(from_f32<bf16>(v));
                     *dst = from_f32<bf16>(clamped_gate(g, to_f32<bf16>(*dst), limit, slope, up_offset));
+                } else if (relu2) {
+                    const float g = fmaxf(to_f32<bf16>(from_f32<bf16>(v)), 0.0f);
+                    *dst = from_f32<bf16>(g * g);
                 } else {
                     *dst = from_f32<bf16>(v);
                 }
@@ -653,8 +705,9 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
 ZI_EXPORT int zi_moe_gemm(const void* A, int a_dtype, long long lda, const int* row_pair, int pairs_per_src,
                           const void* W, int w_dtype, const int* offsets, int n_experts, void* C, int c_dtype,
                           long long ldc, int n_rows, int N, int K, int gated, float limit, float slope, float up_offset,
-                          int allow_tensor_cores, cudaStream_t stream) {
+                          int allow_tensor_cores, const float* a_scale, cudaStream_t stream) {
     if (n_rows <= 0 || N <= 0) return 0;
+    if (gated < 0 || gated > 2) return zi_fail("moe_gemm: unknown activation %d", gated);
     if (K <= 0 || n_experts <= 0) return zi_fail("moe_gemm: K=%d experts=%d", K, n_experts);
     if (row_pair && pairs_per_src <= 0) return zi_fail("moe_gemm: pairs_per_src=%d", pairs_per_src);
     // few rows: the weight-streaming form (allow_tensor_cores & 2 switches it off)
@@ -663,22 +716,22 @@ ZI_EXPORT int zi_moe_gemm(const void* A, int a_dtype, long long lda, const int* 
     const bool all_f32 = a_dtype == ZI_F32 && w_dtype == ZI_F32 && c_dtype == ZI_F32;
     if (n_rows <= 64 && !(allow_tensor_cores & 2) && !all_f32 && (size_t)GV_ROWS * K * sizeof(float) <= 160 * 1024) {
         const size_t smem = (size_t)GV_ROWS * K * sizeof(float);
-        const int cols = GV_WARPS * (gated ? 2 : 4);              // GV_COLS of the kernel that runs
+        const int cols = GV_WARPS * (gated == 1 ? 2 : 4);         // GV_COLS of the kernel that runs
         dim3 grid((N + cols - 1) / cols, n_experts);
         if (grid.y > 65535) return zi_fail("moe_gemm: %d experts are too many for one launch", n_experts);
         ZI_DISPATCH(a_dtype, TA, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(c_dtype, TC, {
-            if (gated) {
+            if (gated == 1) {
                 auto fn = moe_gemv_kernel<TA, TW, TC, true>;
                 if (smem > 48 * 1024 && cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
                     return zi_fail("moe_gemm: cannot reserve %zu bytes of shared memory", smem);
                 fn<<<grid, GV_WARPS * 32, smem, stream>>>((const TA*)A, lda, row_pair, pairs_per_src, (const TW*)W, offsets, (TC*)C,
-                                                          ldc, N, K, limit, slope, up_offset);
+                                                          ldc, N, K, limit, slope, up_offset, a_scale, gated == 2 ? 1 : 0);
             } else {
                 auto fn = moe_gemv_kernel<TA, TW, TC, false>;
                 if (smem > 48 * 1024 && cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
                     return zi_fail("moe_gemm: cannot reserve %zu bytes of shared memory", smem);
                 fn<<<grid, GV_WARPS * 32, smem, stream>>>((const TA*)A, lda, row_pair, pairs_per_src, (const TW*)W, offsets, (TC*)C,
-                                                          ldc, N, K, limit, slope, up_offset);
+                                                          ldc, N, K, limit, slope, up_offset, a_scale, gated == 2 ? 1 : 0);
             }
         });););
         return zi_check_launch("moe_gemm");
@@ -689,7 +742,7 @@ ZI_EXPORT int zi_moe_gemm(const void* A, int a_dtype, long long lda, const int* 
         dim3 grid((N + TN_ - 1) / TN_, (n_rows + TM_ - 1) / TM_ + n_experts);
         if (grid.y > 65535) return zi_fail("moe_gemm: %d rows are too many for one launch", n_rows);
         moe_gemm_mma_kernel<<<grid, 128, 0, stream>>>((const bf16*)A, lda, row_pair, pairs_per_src, (const bf16*)W, offsets,
-                                                      n_experts, (bf16*)C, ldc, N, K, gated, limit, slope, up_offset);
+                                                      n_experts, (bf16*)C, ldc, N, K, gated, limit, slope, up_offset, a_scale);
         return zi_check_launch("moe_gemm");
     }
     dim3 grid((N + GN - 1) / GN, (n_rows + GM - 1) / GM + n_experts);
@@ -697,7 +750,7 @@ ZI_EXPORT int zi_moe_gemm(const void* A, int a_dtype, long long lda, const int* 
     ZI_DISPATCH(a_dtype, TA, ZI_DISPATCH(w_dtype, TW, ZI_DISPATCH(c_dtype, TC, {
         moe_gemm_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>((const TA*)A, lda, row_pair, pairs_per_src, (const TW*)W,
                                                                   offsets, n_experts, (TC*)C, ldc, N, K, gated, limit, slope,
-                                                                  up_offset);
+                                                                  up_offset, a_scale);
     });););
     return zi_check_launch("moe_gemm");
 }
@@ -713,7 +766,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ Y, const int* __restric
         float acc = 0.0f;
         for (int c = 0; c < top; ++c) {
             const int r = pair_row[(size_t)t * top + c];
-            acc = fmaf(wts[(size_t)t * top + c], to_f32<T>(Y[(size_t)r * hidden + j]), acc);
+            acc = fmaf(wts ? wts[(size_t)t * top + c] : 1.0f, to_f32<T>(Y[(size_t)r * hidden + j]), acc);
         }
         if (shared) acc += to_f32<T>(shared[(size_t)t * hidden + j]);
         out[(size_t)t * hidden + j] = from_f32<T>(acc);
@@ -729,7 +782,7 @@ __global__ void moe_combine_vec8_kernel(const T* __restrict__ Y, const int* __re
         float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
         for (int c = 0; c < top; ++c) {
             const int r = pair_row[(size_t)t * top + c];
-            const float wt = wts[(size_t)t * top + c];
+            const float wt = wts ? wts[(size_t)t * top + c] : 1.0f;
             float v[8];
             load8(Y + (size_t)r * hidden + j, v);
 #pragma unroll

@@ -196,3 +196,203 @@ ZI_EXPORT int zi_rmsnorm_append(const void* x, int x_dtype, long long row_stride
     });););
     return zi_check_launch("rmsnorm_append");
 }
+
+// ---------------------------------------------------------------------------------------
+// Rotation by position of a span of every head, in either pairing, with the cache append of keys and values.
+//   x       [n_tokens, ldx]: n_q query heads, then n_k key heads, then (v_mode 1) n_k value heads, head_dim each
+//   span    entries rot_offset .. rot_offset + rot_dims - 1 of a head turn, the rest pass unchanged
+//   pairing interleaved 0: entry i pairs with i + rot_dims / 2;  1: entry 2i with 2i + 1  (i < rot_dims / 2)
+//           (lo, hi) -> (lo cos a - hi sin a, hi cos a + lo sin a),  a = float(pos) * inv_freq[i]
+//   q_out   [n_tokens, ldq] receives the query heads (may be x itself: a pair is read and written by one thread)
+//   cache   null, or a paged cache with two planes: rotated keys go to the first; the second receives the value heads
+//           (v_mode 1) or the keys as they were before the rotation (v_mode 2: the values are the unrotated keys)
+// One block per token; a thread takes a pair of the span or a single entry outside it.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void rotate_pair(float lo, float hi, float c, float s, float* olo, float* ohi) {
+    *olo = __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, s));
+    *ohi = __fadd_rn(__fmul_rn(hi, c), __fmul_rn(lo, s));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotary_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ q_out, long long ldq, T* __restrict__ cache,
+              const int* __restrict__ tables, const int* __restrict__ tok_seg, const int* __restrict__ pos,
+              const float* __restrict__ inv_freq, int n_q, int n_k, int head_dim, int rot_offset, int rot_dims,
+              int interleaved, int v_mode, int page_size, int max_blocks, long long page_stride, long long kv_stride) {
+    extern __shared__ float cs[];            // cos[half], sin[half]
+    const int n = blockIdx.x;
+    const int half = rot_dims >> 1;
+    const int p = pos[n];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)p * inv_freq[i], &s, &c);
+        cs[i] = c;
+        cs[half + i] = s;
+    }
+    __syncthreads();
+    T* page_base = nullptr;
+    if (cache) {
+        const int seg = tok_seg ? tok_seg[n] : n;
+        const int page = tables[(size_t)seg * max_blocks + p / page_size];
+        page_base = cache + (size_t)page * page_stride + (size_t)(p % page_size) * head_dim;
+    }
+    const T* row = x + (size_t)n * ldx;
+    const int per_head = head_dim - half;                      // pairs of the span, then the singles outside it
+    const int heads = n_q + (cache ? n_k * (v_mode == 1 ? 2 : 1) : 0);
+    for (int idx = threadIdx.x; idx < heads * per_head; idx += blockDim.x) {
+        const int h = idx / per_head, it = idx - h * per_head;
+        const T* src = row + (size_t)h * head_dim;
+        T* dst;
+        T* raw = nullptr;                                      // where the unrotated copy of a key goes (v_mode 2)
+        bool turn = true;
+        if (h < n_q) {
+            dst = q_out + (size_t)n * ldq + (size_t)h * head_dim;
+        } else if (h < n_q + n_k) {
+            dst = page_base + (size_t)(h - n_q) * page_size * head_dim;
+            if (v_mode == 2) raw = dst + kv_stride;
+        } else {
+            dst = page_base + kv_stride + (size_t)(h - n_q - n_k) * page_size * head_dim;
+            turn = false;
+        }
+        if (it < half) {
+            const int lo_at = rot_offset + (interleaved ? 2 * it : it), hi_at = rot_offset + (interleaved ? 2 * it + 1 : it + half);
+            const T lo_raw = src[lo_at], hi_raw = src[hi_at];
+            if (raw) { raw[lo_at] = lo_raw; raw[hi_at] = hi_raw; }
+            if (turn) {
+                float olo, ohi;
+                rotate_pair(to_f32<T>(lo_raw), to_f32<T>(hi_raw), cs[it], cs[half + it], &olo, &ohi);
+                dst[lo_at] = from_f32<T>(olo);
+                dst[hi_at] = from_f32<T>(ohi);
+            } else {
+                dst[lo_at] = lo_raw;
+                dst[hi_at] = hi_raw;
+            }
+        } else {
+            int d = it - half;                                 // the (it - half)-th entry outside the span
+            if (d >= rot_offset) d += rot_dims;
+            const T v = src[d];
+            if (raw) raw[d] = v;
+            if (dst != src) dst[d] = v;
+        }
+    }
+}
+
+ZI_EXPORT int zi_rotary(const void* x, int dtype, long long ldx, void* q_out, long long ldq, void* cache, const int* tables,
+                        const int* tok_seg, const int* pos, const float* inv_freq, int n_tokens, int n_q, int n_k, int head_dim,
+                        int rot_offset, int rot_dims, int interleaved, int v_mode, int page_size, int max_blocks,
+                        long long page_stride, long long kv_stride, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (head_dim <= 0 || rot_dims < 0 || (rot_dims & 1) || rot_offset < 0 || rot_offset + rot_dims > head_dim)
+        return zi_fail("rotary: a span of %d entries from %d does not fit a head of %d (or is odd)", rot_dims, rot_offset, head_dim);
+    if (n_q < 0 || n_k < 0 || v_mode < 0 || v_mode > 2) return zi_fail("rotary: bad head counts or value mode");
+    if (cache && (page_size <= 0 || max_blocks <= 0 || !tables)) return zi_fail("rotary: the cache append needs tables and a page size");
+    if (cache && v_mode == 2 && kv_stride == 0) return zi_fail("rotary: unrotated keys as values need a second plane");
+    const size_t smem = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
+    ZI_DISPATCH(dtype, T, {
+        rotary_kernel<T><<<n_tokens, 256, smem, stream>>>((const T*)x, ldx, (T*)q_out, ldq, (T*)cache, tables, tok_seg, pos, inv_freq,
+                                                          n_q, n_k, head_dim, rot_offset, rot_dims, interleaved, v_mode, page_size,
+                                                          max_blocks, page_stride, kv_stride);
+    });
+    return zi_check_launch("rotary");
+}
+
+// ---------------------------------------------------------------------------------------
+// The latents of a latent-attention layer whose keys carry a rotated part, from one row of a stacked product:
+//   cq_out[n, :]              = rmsnorm(x[n, q_off .. q_off + q_rank)) * gq               (q_rank 0: no query latent)
+//   cache row of token n      = [ rmsnorm(x[n, c_off .. c_off + rank)) * gc | turn(x[n, c_off + rank .. + rot_dim)) | 0 .. ]
+// The cache has one plane and one head of `row_width` >= rank + rot_dim entries per token; what lies behind rank + rot_dim is
+// never written (the pool is zeroed when it is made).  The turned part: the first rot_dims of its rot_dim entries, paired as
+// in rotary_kernel.  One block per token.
+// ---------------------------------------------------------------------------------------
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128)
+latent_prepare_kernel(const T* __restrict__ x, long long ldx, int q_off, int q_rank, const TW* __restrict__ gq,
+                      T* __restrict__ cq_out, int c_off, int rank, const TW* __restrict__ gc, int rot_dim, int rot_dims,
+                      int interleaved, const float* __restrict__ inv_freq, float eps, T* __restrict__ cache, int row_width,
+                      const int* __restrict__ tables, const int* __restrict__ tok_seg, const int* __restrict__ pos,
+                      int page_size, int max_blocks, long long page_stride) {
+    __shared__ float scratch[32];
+    const int n = blockIdx.x;
+    const T* xr = x + (size_t)n * ldx;
+    if (q_rank > 0) {
+        float ss = 0.0f;
+        for (int j = threadIdx.x; j < q_rank; j += blockDim.x) {
+            const float v = to_f32<T>(xr[q_off + j]);
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float rstd = 1.0f / sqrtf(ss / (float)q_rank + eps);
+        for (int j = threadIdx.x; j < q_rank; j += blockDim.x)
+            cq_out[(size_t)n * q_rank + j] = from_f32<T>((to_f32<TW>(gq[j]) * to_f32<T>(xr[q_off + j])) * rstd);
+    }
+    if (!cache) return;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) {
+        const float v = to_f32<T>(xr[c_off + j]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)rank + eps);
+    const int p = pos[n];
+    const int seg = tok_seg ? tok_seg[n] : n;
+    const int page = tables[(size_t)seg * max_blocks + p / page_size];
+    T* dst = cache + (long long)page * page_stride + (long long)(p % page_size) * row_width;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) dst[j] = from_f32<T>((to_f32<TW>(gc[j]) * to_f32<T>(xr[c_off + j])) * rstd);
+    const int half = rot_dims >> 1;
+    const T* kr = xr + c_off + rank;
+    for (int it = threadIdx.x; it < rot_dim - half; it += blockDim.x) {
+        if (it < half) {
+            const int lo_at = interleaved ? 2 * it : it, hi_at = interleaved ? 2 * it + 1 : it + half;
+            float s, c, olo, ohi;
+            sincosf((float)p * inv_freq[it], &s, &c);
+            rotate_pair(to_f32<T>(kr[lo_at]), to_f32<T>(kr[hi_at]), c, s, &olo, &ohi);
+            dst[rank + lo_at] = from_f32<T>(olo);
+            dst[rank + hi_at] = from_f32<T>(ohi);
+        } else {
+            const int d = it - half + rot_dims;
+            dst[rank + d] = kr[d];
+        }
+    }
+}
+
+ZI_EXPORT int zi_latent_prepare(const void* x, int dtype, long long ldx, int q_off, int q_rank, const void* gq, void* cq_out,
+                                int c_off, int rank, const void* gc, int w_dtype, int rot_dim, int rot_dims, int interleaved,
+                                const float* inv_freq, float eps, void* cache, int row_width, const int* tables,
+                                const int* tok_seg, const int* pos, int n_tokens, int page_size, int max_blocks,
+                                long long page_stride, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (q_rank < 0 || rank <= 0 || rot_dim < 0 || rot_dims < 0 || (rot_dims & 1) || rot_dims > rot_dim)
+        return zi_fail("latent_prepare: q_rank=%d rank=%d rot_dim=%d rot_dims=%d", q_rank, rank, rot_dim, rot_dims);
+    if (cache && (row_width < rank + rot_dim || page_size <= 0 || max_blocks <= 0))
+        return zi_fail("latent_prepare: a cache row of %d entries cannot hold %d + %d", row_width, rank, rot_dim);
+    ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {
+        latent_prepare_kernel<T, TW><<<n_tokens, 128, 0, stream>>>((const T*)x, ldx, q_off, q_rank, (const TW*)gq, (T*)cq_out, c_off,
+                                                                   rank, (const TW*)gc, rot_dim, rot_dims, interleaved, inv_freq, eps,
+                                                                   (T*)cache, row_width, tables, tok_seg, pos, page_size, max_blocks,
+                                                                   page_stride);
+    }););
+    return zi_check_launch("latent_prepare");
+}
+
+// ---------------------------------------------------------------------------------------
+// Output gate: a[n, j] *= sigmoid(g[n, j]), float32 inside; the rows of g may be strided (a slice of a wider product).
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void sigmoid_mul_kernel(T* __restrict__ a, const T* __restrict__ g, long long ldg, int width, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / width;
+        const int j = (int)(i - n * width);
+        const float gv = to_f32<T>(g[n * ldg + j]);
+        a[i] = from_f32<T>(to_f32<T>(a[i]) / (1.0f + expf(-gv)));
+    }
+}
+
+ZI_EXPORT int zi_sigmoid_mul(void* a, const void* g, int dtype, long long ldg, int rows, int width, cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    const size_t total = (size_t)rows * width;
+    const size_t want = (total + 255) / 256;
+    ZI_DISPATCH(dtype, T, {
+        sigmoid_mul_kernel<T><<<(int)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>((T*)a, (const T*)g, ldg, width, total);
+    });
+    return zi_check_launch("sigmoid_mul");
+}

@@ -7,6 +7,7 @@ from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
 
+from .. import ops
 from ..cache.manager import CallCacheView
 from ..config.spec import ModelSpec
 from ..config.spec import PartSpec
@@ -36,6 +37,7 @@ class Model:
         self.head = build_part("head", spec.head or PartSpec("output_head", {
             "vocab_size": spec.vocab_size, "hidden_size": spec.hidden_size, "tied": spec.tie_word_embeddings,
             "name": spec.head_name}))
+        self._keeps_embedding = any(call.add_embedding for call in spec.schedule)
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
         self._views_of: Optional[Mapping[object, CallCacheView]] = None
@@ -106,10 +108,14 @@ class Model:
         h = torch.empty((ctx.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
         self.embedding.forward_step(ctx, h)
         stream = ResidualStream(h)
+        embedded = h.clone() if self._keeps_embedding else None        # for the calls that add it again
         if self._views_of is not cache_views:          # the same mapping step after step: resolve the keys once
             self._views_by_call = [{role: cache_views[key] for role, key in keys.items()} for keys in self._call_caches]
             self._views_of = cache_views
         for pos, call in enumerate(self.spec.schedule):
+            if call.add_embedding:
+                # float32; a branch output that is still pending joins at the next norm, and sums commute up to rounding
+                ops.add(stream.h, embedded, stream.h)
             self.blocks[call.layer].forward(stream, ctx, self._views_by_call[pos], owns_cache=call.cache_of is None)
         if logit_rows is None or logit_rows.numel() == 0:
             return None

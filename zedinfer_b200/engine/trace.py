@@ -20,7 +20,7 @@ import sys
 from typing import List, Optional
 
 PAGE_SIZE = 16
-MAX_LIVE = 8
+MAX_LIVE = 4          # live requests at any time: the state slots, and the pools of windowed groups, are made for this many
 
 
 def build_parser() -> argparse.ArgumentParser:

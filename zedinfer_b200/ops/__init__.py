@@ -12,7 +12,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ._lib import (BF16, F32, KernelError, Library, c_float, c_int, c_ll, dtype_code, need_contiguous, need_cuda,
+from ._lib import (BF16, F32, KernelError, Library, c_float, c_int, c_ll, c_void_p, dtype_code, need_contiguous, need_cuda,
                    need_int32, ptr, stream)
 
 # Library products keep float32 sums: without this cuBLAS may pick split-K kernels that add partial sums in bfloat16.
@@ -28,13 +28,15 @@ _gemm_tcgen05 = Library("gemm_tcgen05")
 _attention_tcgen05 = Library("attention_tcgen05")
 _rowwise = Library("rowwise")
 _moe = Library("moe")
+_ssm = Library("ssm")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "rope_table", "gemm_smallm_rope", "can_fuse_rope_product", "silu_mul", "add", "cast",
            "gemm_nt", "linear", "linear_for_residual", "gemm_smallm", "gemm_tcgen05", "gemm_tcgen05_tiles", "tcgen05_status", "status_word", "linear_silu_mul", "raise_if_tcgen05_failed", "paged_attention", "attention", "decode_attention", "decode_attention_tma", "prefill_attention", "prefill_attention_tcgen05", "argmax", "sample", "repetition_penalty", "advance_decode",
            "embedding_positions", "softcap", "relu2", "gated_clamp_mul", "rmsnorm_append", "linear_per_head", "route_topk",
            "moe_group", "moe_gemm", "moe_combine", "linear_gated_clamp_mul", "linear_relu2", "moe_group_padded",
-           "moe_gather_rows", "gemm_tcgen05_grouped", "route"]
+           "moe_gather_rows", "gemm_tcgen05_grouped", "route", "rotary", "latent_prepare", "sigmoid_mul", "segment_bounds",
+           "causal_conv_silu", "conv_state_update", "ssm_scan", "gated_group_rmsnorm"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -917,22 +919,27 @@ def linear_per_head(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None
 
 
 # ---- routed feed-forward, csrc/moe.cu ------------------------------------------------------------------------------
-def route_topk(logits: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor) -> None:
+ROUTER_SCORES = {"softmax_chosen": 0, "sigmoid": 1}
+
+
+def route_topk(logits: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, score: str = "softmax_chosen") -> None:
     """Per row of float32 ``logits [tokens, experts]``: the ``top`` largest (lowest index wins a tie) into ``idx`` (int32
-    ``[tokens, top]``, largest first) and the softmax over those alone into ``wts`` (float32)."""
+    ``[tokens, top]``, largest first) and their weights into ``wts`` (float32): the softmax over those alone
+    (``score="softmax_chosen"``), or each one's own ``sigmoid(logit)``, not renormalised (``"sigmoid"``)."""
     need_cuda(logits, idx, wts)
     need_int32("idx", idx)
     need_contiguous("logits", logits), need_contiguous("idx", idx), need_contiguous("wts", wts)
     n, e = logits.shape
     if logits.dtype != torch.float32 or wts.dtype != torch.float32 or idx.shape != (n, top) or wts.shape != (n, top):
         raise KernelError(f"route_topk: logits {tuple(logits.shape)} {logits.dtype}, idx {tuple(idx.shape)}, wts {tuple(wts.shape)}")
-    _moe.call("zi_route_topk", ptr(logits), c_int(n), c_int(e), c_int(top), ptr(idx), ptr(wts), stream())
+    _moe.call("zi_route_topk", ptr(logits), c_int(n), c_int(e), c_int(top), ptr(idx), ptr(wts), c_int(ROUTER_SCORES[score]), stream())
 
 
 def route(x: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor,
-          wts: torch.Tensor, logits: Optional[torch.Tensor] = None) -> None:
+          wts: torch.Tensor, logits: Optional[torch.Tensor] = None, score: str = "softmax_chosen") -> None:
     """The router in one kernel: float32 logits ``x @ w_router.T + bias`` (operands of any storage type, float32 sums in
-    a fixed order), then as :func:`route_topk`.  ``logits``: optional float32 ``[tokens, experts]`` to receive them."""
+    a fixed order), then as :func:`route_topk` (``score`` as there).  ``logits``: optional float32 ``[tokens, experts]`` to
+    receive them."""
     need_cuda(x, w_router, bias, idx, wts, logits)
     need_int32("idx", idx)
     need_contiguous("w_router", w_router), need_contiguous("idx", idx), need_contiguous("wts", wts)
@@ -943,7 +950,8 @@ def route(x: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor],
             or (logits is not None and (logits.dtype != torch.float32 or logits.shape != (n, e) or not logits.is_contiguous()))):
         raise KernelError(f"route: x {tuple(x.shape)}, w_router {tuple(w_router.shape)}, idx {tuple(idx.shape)}, wts {tuple(wts.shape)}")
     _moe.call("zi_route", ptr(x), c_int(dtype_code(x.dtype)), c_ll(x.stride(0)), ptr(w_router), c_int(dtype_code(w_router.dtype)),
-              ptr(bias), c_int(n), c_int(k), c_int(e), c_int(top), ptr(idx), ptr(wts), ptr(logits), stream())
+              ptr(bias), c_int(n), c_int(k), c_int(e), c_int(top), ptr(idx), ptr(wts), ptr(logits), c_int(ROUTER_SCORES[score]),
+              stream())
 
 
 def moe_group(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, row_pair: torch.Tensor, pair_row: torch.Tensor) -> None:
@@ -974,27 +982,33 @@ def moe_group_padded(idx: torch.Tensor, n_experts: int, pad: int, starts: torch.
               ptr(row_pair), ptr(pair_row), ptr(tile_expert), stream())
 
 
-def moe_gather_rows(x: torch.Tensor, row_pair: torch.Tensor, pairs_per_src: int, out: torch.Tensor) -> None:
-    """``out[r] = x[row_pair[r] // pairs_per_src]``, zeros where ``row_pair[r]`` is negative (bfloat16)."""
-    need_cuda(x, row_pair, out)
+def moe_gather_rows(x: torch.Tensor, row_pair: torch.Tensor, pairs_per_src: int, out: torch.Tensor,
+                    scale: Optional[torch.Tensor] = None) -> None:
+    """``out[r] = x[row_pair[r] // pairs_per_src]``, zeros where ``row_pair[r]`` is negative (bfloat16).  ``scale``: float32,
+    one per pair; the row of pair ``row_pair[r]`` is multiplied by ``scale[row_pair[r]]`` and rounded once."""
+    need_cuda(x, row_pair, out, scale)
+    if scale is not None and (scale.dtype != torch.float32 or not scale.is_contiguous()):
+        raise KernelError("moe_gather_rows: scale must be contiguous float32, one per pair")
     need_int32("row_pair", row_pair), need_contiguous("out", out)
     if x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or x.stride(1) != 1 or out.shape != (row_pair.numel(), x.shape[1]):
         raise KernelError(f"moe_gather_rows: x {tuple(x.shape)} {x.dtype}, out {tuple(out.shape)}, {row_pair.numel()} rows")
     _moe.call("zi_moe_gather_rows", ptr(x), c_ll(x.stride(0)), ptr(row_pair), c_int(pairs_per_src), ptr(out), c_int(out.shape[0]),
-              c_int(x.shape[1]), stream())
+              c_int(x.shape[1]), ptr(scale), stream())
 
 
 GROUPED_TILE_ROWS = 128          # rows of a tile of the tcgen05 grouped product: groups are padded to whole tiles
 
 
 def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor,
-                         gated: Optional[tuple] = None) -> None:
+                         gated: Optional[tuple] = None, relu2: bool = False) -> None:
     """Grouped product on the tcgen05 tensor cores: ``x`` holds every group's rows one after the other, padded to
     whole tiles of 128 rows; row tile t takes the weight ``w[tile_expert[t]]`` (``w`` is ``[experts, N, K]``, or with
     ``gated = (limit, slope, up_offset)`` ``[experts, 2 N, K]`` and the clamped, gated activation in the epilogue); a
-    negative entry skips the tile.  ``out [rows, N]`` row by row as ``x``.  A bounded wait that runs out is reported by
-    :func:`tcgen05_status`."""
+    negative entry skips the tile.  ``relu2``: ``out = max(x @ w.T, 0)^2``.  ``out [rows, N]`` row by row as ``x``.  A
+    bounded wait that runs out is reported by :func:`tcgen05_status`."""
     need_cuda(x, w, tile_expert, out)
+    if gated and relu2:
+        raise KernelError("gemm_tcgen05_grouped: one activation at a time")
     need_int32("tile_expert", tile_expert)
     need_contiguous("w", w), need_contiguous("tile_expert", tile_expert)
     m, k = x.shape
@@ -1008,7 +1022,7 @@ def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Te
         raise KernelError("gemm_tcgen05_grouped: bfloat16 operands only")
     limit, slope, up_offset = gated if gated else (0.0, 0.0, 0.0)
     _gemm_tcgen05.call("zi_gemm_tcgen05_grouped", ptr(x), ptr(w), ptr(out), c_int(dtype_code(out.dtype)), ptr(_tc_status(x.device)),
-                       c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(out.stride(0)), c_int(2 if gated else 0), c_int(e),
+                       c_int(m), c_int(n), c_int(k), c_ll(x.stride(0)), c_ll(out.stride(0)), c_int(2 if gated else (3 if relu2 else 0)), c_int(e),
                        ptr(tile_expert), c_int(_num_sms(x.device)), c_float(limit), c_float(slope), c_float(up_offset), stream())
     _tc_launched[x.device] = True
 
@@ -1019,12 +1033,19 @@ MOE_TCGEN05_MIN_PAIRS = 65       # from this many (token, choice) pairs the grou
 
 
 def moe_gemm(a: torch.Tensor, row_pair: Optional[torch.Tensor], pairs_per_src: int, w: torch.Tensor, offsets: torch.Tensor,
-             out: torch.Tensor, gated: Optional[tuple] = None) -> None:
+             out: torch.Tensor, gated: Optional[tuple] = None, relu2: bool = False,
+             a_scale: Optional[torch.Tensor] = None) -> None:
     """Grouped product over the sorted rows of every expert: ``out[r] = a[src(r)] @ w[e(r)].T``; ``src(r) = row_pair[r]
     // pairs_per_src`` (``row_pair`` None: r itself), ``e(r)`` from ``offsets``.  ``w`` is ``[experts, N, K]``, or with
     ``gated = (limit, slope, up_offset)`` ``[experts, 2 N, K]`` (gate rows, then up rows) and ``out`` the clamped, gated
-    product of the two halves (see :func:`gated_clamp_mul`)."""
-    need_cuda(a, row_pair, w, offsets, out)
+    product of the two halves (see :func:`gated_clamp_mul`).  ``relu2``: ``out = max(product, 0)^2``.  ``a_scale``: float32,
+    one per pair; the row of ``a`` that sorted row r reads is multiplied by ``a_scale[row_pair[r]]`` (``row_pair`` None:
+    ``a_scale[r]``) and rounded to ``a``'s type before the product (a router weight on the expert's input)."""
+    need_cuda(a, row_pair, w, offsets, out, a_scale)
+    if gated and relu2:
+        raise KernelError("moe_gemm: one activation at a time")
+    if a_scale is not None and (a_scale.dtype != torch.float32 or not a_scale.is_contiguous()):
+        raise KernelError("moe_gemm: a_scale must be contiguous float32, one per pair")
     need_int32("offsets", offsets)
     need_contiguous("w", w), need_contiguous("out", out)
     if row_pair is not None:
@@ -1036,22 +1057,181 @@ def moe_gemm(a: torch.Tensor, row_pair: Optional[torch.Tensor], pairs_per_src: i
     limit, slope, up_offset = gated if gated else (0.0, 0.0, 0.0)
     _moe.call("zi_moe_gemm", ptr(a), c_int(dtype_code(a.dtype)), c_ll(a.stride(0)), ptr(row_pair), c_int(pairs_per_src), ptr(w),
               c_int(dtype_code(w.dtype)), ptr(offsets), c_int(e), ptr(out), c_int(dtype_code(out.dtype)), c_ll(out.stride(0)),
-              c_int(rows), c_int(n), c_int(k), c_int(1 if gated else 0), c_float(limit), c_float(slope), c_float(up_offset),
-              c_int((1 if MOE_TENSOR_CORES else 0) | (0 if MOE_FEW_ROWS_STREAMING else 2)), stream())
+              c_int(rows), c_int(n), c_int(k), c_int(1 if gated else (2 if relu2 else 0)), c_float(limit), c_float(slope),
+              c_float(up_offset), c_int((1 if MOE_TENSOR_CORES else 0) | (0 if MOE_FEW_ROWS_STREAMING else 2)), ptr(a_scale),
+              stream())
 
 
-def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, wts: torch.Tensor, shared: Optional[torch.Tensor],
+def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, wts: Optional[torch.Tensor], shared: Optional[torch.Tensor],
                 out: torch.Tensor) -> None:
     """``out[t] = sum_j wts[t, j] * y[pair_row[t, j]] (+ shared[t])``, j rising, in float32 with one rounding.  ``y`` has
-    a row per pair, or more where the sorted rows are padded."""
+    a row per pair, or more where the sorted rows are padded.  ``wts`` None: every weight is 1 (``pair_row`` is then
+    ``[tokens, top]``)."""
     need_cuda(y, pair_row, wts, shared, out)
     need_int32("pair_row", pair_row)
-    need_contiguous("y", y), need_contiguous("pair_row", pair_row), need_contiguous("wts", wts), need_contiguous("out", out)
+    need_contiguous("y", y), need_contiguous("pair_row", pair_row), need_contiguous("out", out)
     n, hidden = out.shape
-    top = wts.shape[1]
-    if wts.dtype != torch.float32 or wts.shape != (n, top) or pair_row.numel() != n * top or y.dim() != 2 or y.shape[0] < n * top or y.shape[1] != hidden \
+    if wts is None:
+        top = pair_row.numel() // max(n, 1)
+    else:
+        need_contiguous("wts", wts)
+        top = wts.shape[1]
+    if (wts is not None and (wts.dtype != torch.float32 or wts.shape != (n, top))) or pair_row.numel() != n * top or y.dim() != 2 or y.shape[0] < n * top or y.shape[1] != hidden \
             or y.dtype != out.dtype or (shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype
                                                                 or not shared.is_contiguous())):
-        raise KernelError(f"moe_combine: y {tuple(y.shape)}, wts {tuple(wts.shape)}, out {tuple(out.shape)} do not agree")
+        raise KernelError(f"moe_combine: y {tuple(y.shape)}, {n} x {top} weights, out {tuple(out.shape)} do not agree")
     _moe.call("zi_moe_combine", ptr(y), ptr(pair_row), ptr(wts), ptr(shared), ptr(out), c_int(dtype_code(out.dtype)), c_int(n),
               c_int(top), c_int(hidden), stream())
+
+
+# ---- rotation of a span of every head, latents with a rotated key part, output gate: csrc/rowwise.cu ------------------------
+def rotary(x: torch.Tensor, q_out: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, n_q: int, n_k: int, head_dim: int,
+           rot_offset: int, rot_dims: int, interleaved: bool, cache=None, tables: Optional[torch.Tensor] = None,
+           tok_seg: Optional[torch.Tensor] = None, v_mode: int = 0) -> None:
+    """Turn entries ``rot_offset .. rot_offset + rot_dims`` of every query and key head of ``x`` (``[tokens, (n_q + n_k
+    [+ n_k]) * head_dim]``, rows may be strided) by the token's position; entry i of the span pairs with ``i + rot_dims /
+    2``, or with ``interleaved`` entry 2i with 2i + 1; the angle of pair i is ``float(pos) * inv_freq[i]``.  Queries go to
+    ``q_out`` (``[tokens, n_q * head_dim]``; may be ``x`` itself).  ``cache`` (a CallCacheView with two planes): turned keys
+    are appended to the first plane and, by ``v_mode``, the value heads of ``x`` (1) or the keys as they were before the
+    turn (2) to the second."""
+    need_cuda(x, q_out, pos, inv_freq, tables, tok_seg)
+    need_int32("pos", pos)
+    n = x.shape[0]
+    if x.stride(1) != 1 or q_out.stride(-1) != 1 or q_out.dtype != x.dtype:
+        raise KernelError("rotary: rows of x and q_out must be contiguous and of one type")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2 or not inv_freq.is_contiguous():
+        raise KernelError(f"rotary: inv_freq must be float32 with {rot_dims // 2} entries")
+    ct = None
+    if cache is not None:
+        ct = cache.tensor
+        if tables is None or ct.dtype != x.dtype:
+            raise KernelError("rotary: the cache append needs block tables and a cache of x's type")
+        need_int32("tables", tables)
+    q2 = q_out.view(n, -1) if q_out.dim() == 3 else q_out
+    _rowwise.call("zi_rotary", ptr(x), c_int(dtype_code(x.dtype)), c_ll(x.stride(0)), ptr(q2), c_ll(q2.stride(0)), ptr(ct),
+                  ptr(tables), ptr(tok_seg), ptr(pos), ptr(inv_freq), c_int(n), c_int(n_q), c_int(n_k if cache is not None else 0),
+                  c_int(head_dim), c_int(rot_offset), c_int(rot_dims), c_int(1 if interleaved else 0), c_int(v_mode),
+                  c_int(cache.page_size if cache is not None else 0), c_int(tables.shape[1] if tables is not None else 0),
+                  c_ll(cache.page_stride if cache is not None else 0), c_ll(cache.kv_stride if cache is not None else 0), stream())
+
+
+def latent_prepare(x: torch.Tensor, q_off: int, q_rank: int, gq: Optional[torch.Tensor], cq_out: Optional[torch.Tensor],
+                   c_off: int, rank: int, gc: torch.Tensor, rot_dim: int, rot_dims: int, interleaved: bool,
+                   inv_freq: Optional[torch.Tensor], eps: float, cache, tables: torch.Tensor, tok_seg: Optional[torch.Tensor],
+                   pos: torch.Tensor) -> None:
+    """From each row of ``x`` (a stacked product, rows may be strided): ``cq_out[n] = rmsnorm(x[n, q_off : q_off + q_rank])
+    * gq`` (``q_rank`` 0: none), and into the row of token n in ``cache`` (one plane, one head, ``cache.tensor.shape[-1]``
+    entries) ``rmsnorm(x[n, c_off : c_off + rank]) * gc`` followed by the next ``rot_dim`` entries of ``x`` with their first
+    ``rot_dims`` turned by the token's position (pairing and angles as :func:`rotary`).  ``cache`` None: only the query
+    latent."""
+    need_cuda(x, gq, cq_out, gc, inv_freq, tables, tok_seg, pos)
+    need_int32("pos", pos)
+    if x.stride(1) != 1 or (cq_out is not None and (not cq_out.is_contiguous() or cq_out.dtype != x.dtype)):
+        raise KernelError("latent_prepare: rows of x must be contiguous, cq_out contiguous and of x's type")
+    if q_rank and (gq is None or cq_out is None or gq.dtype != gc.dtype):
+        raise KernelError("latent_prepare: a query latent needs its weight and an output")
+    if rot_dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2):
+        raise KernelError(f"latent_prepare: inv_freq must be float32 with {rot_dims // 2} entries")
+    ct = cache.tensor if cache is not None else None
+    if ct is not None and ct.dtype != x.dtype:
+        raise KernelError("latent_prepare: the cache must have x's type")
+    _rowwise.call("zi_latent_prepare", ptr(x), c_int(dtype_code(x.dtype)), c_ll(x.stride(0)), c_int(q_off), c_int(q_rank), ptr(gq),
+                  ptr(cq_out), c_int(c_off), c_int(rank), ptr(gc), c_int(dtype_code(gc.dtype)), c_int(rot_dim), c_int(rot_dims),
+                  c_int(1 if interleaved else 0), ptr(inv_freq), c_float(eps), ptr(ct), c_int(ct.shape[-1] if ct is not None else 0),
+                  ptr(tables), ptr(tok_seg), ptr(pos), c_int(x.shape[0]), c_int(cache.page_size if cache is not None else 0),
+                  c_int(tables.shape[1] if tables is not None else 0), c_ll(cache.page_stride if cache is not None else 0), stream())
+
+
+def sigmoid_mul(a: torch.Tensor, g: torch.Tensor) -> None:
+    """In place: ``a *= sigmoid(g)`` (float32 inside); ``g [rows, width]`` may have strided rows."""
+    need_cuda(a, g)
+    need_contiguous("a", a)
+    if a.dim() != 2 or g.shape != a.shape or g.stride(1) != 1 or g.dtype != a.dtype:
+        raise KernelError(f"sigmoid_mul: a {tuple(a.shape)} and g {tuple(g.shape)} must agree")
+    _rowwise.call("zi_sigmoid_mul", ptr(a), ptr(g), c_int(dtype_code(a.dtype)), c_ll(g.stride(0)), c_int(a.shape[0]), c_int(a.shape[1]),
+                  stream())
+
+
+# ---- selective state-space mixer, csrc/ssm.cu ----------------------------------------------------------------------------------
+def segment_bounds(tok_seg: torch.Tensor, n_segments: int, out: torch.Tensor) -> None:
+    """``out[s] = (first token, one past the last token)`` of segment s (int32 ``[segments, 2]``) from the token -> segment
+    map of a step whose segments are runs of consecutive tokens."""
+    need_cuda(tok_seg, out)
+    need_int32("tok_seg", tok_seg), need_int32("out", out)
+    need_contiguous("tok_seg", tok_seg), need_contiguous("out", out)
+    if out.numel() != 2 * n_segments:
+        raise KernelError("segment_bounds: out must be [segments, 2]")
+    _ssm.call("zi_segment_bounds", ptr(tok_seg), c_int(tok_seg.numel()), c_int(n_segments), ptr(out), stream())
+
+
+def _state_args(state: torch.Tensor, offset: int):
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1:
+        raise KernelError("a state slot pool must be float32 [slots, entries]")
+    return c_void_p(state.data_ptr() + 4 * offset), c_ll(state.stride(0))
+
+
+def causal_conv_silu(u: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, state_offset: int,
+                     slots: torch.Tensor, tok_seg: Optional[torch.Tensor], pos: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[n, c] = silu(bias[c] + sum_j w[c, j] * u_c(pos[n] - (taps - 1) + j))``: a causal convolution per channel over
+    each request's tokens.  Inputs of this step come from ``u`` (``[tokens, channels]``, rows may be strided), earlier ones
+    from the request's slot of ``state`` (float32 ``[slots, entries]``; the ring ``[taps - 1, channels]`` starts at entry
+    ``state_offset``), and what lies before position 0 is zero.  ``tok_seg`` None: token n is segment n."""
+    need_cuda(u, w, bias, state, slots, tok_seg, pos, out)
+    need_int32("slots", slots), need_int32("pos", pos)
+    need_contiguous("w", w), need_contiguous("out", out)
+    n, ch = u.shape
+    if u.stride(1) != 1 or w.shape[0] != ch or out.shape != (n, ch) or out.dtype != u.dtype or (bias is not None and (bias.numel() != ch or bias.dtype != w.dtype)):
+        raise KernelError(f"causal_conv_silu: u {tuple(u.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+    sp, ss = _state_args(state, state_offset)
+    _ssm.call("zi_causal_conv_silu", ptr(u), c_int(dtype_code(u.dtype)), c_ll(u.stride(0)), ptr(w), ptr(bias), c_int(dtype_code(w.dtype)),
+              sp, ss, ptr(slots), ptr(tok_seg), ptr(pos), ptr(out), c_int(n), c_int(ch), c_int(w.shape[1]), stream())
+
+
+def conv_state_update(u: torch.Tensor, taps: int, state: torch.Tensor, state_offset: int, slots: torch.Tensor,
+                      bounds: Optional[torch.Tensor], pos: torch.Tensor, n_segments: int) -> None:
+    """The last ``taps - 1`` inputs of every segment go into its slot's ring (the input at position q into row ``q mod
+    (taps - 1)``).  ``bounds`` from :func:`segment_bounds`; None: segment s is token s."""
+    need_cuda(u, state, slots, bounds, pos)
+    need_int32("slots", slots), need_int32("pos", pos)
+    if u.stride(1) != 1:
+        raise KernelError("conv_state_update: rows of u must be contiguous")
+    sp, ss = _state_args(state, state_offset)
+    _ssm.call("zi_conv_state_update", ptr(u), c_int(dtype_code(u.dtype)), c_ll(u.stride(0)), sp, ss, ptr(slots), ptr(bounds), ptr(pos),
+              c_int(n_segments), c_int(u.shape[1]), c_int(taps), stream())
+
+
+def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, slots: torch.Tensor, bounds: Optional[torch.Tensor], y: torch.Tensor, n_segments: int,
+             heads: int, vdim: int, n_state: int, groups: int) -> None:
+    """The recurrence of a selective state-space layer over each segment's tokens in order, float32 throughout:
+    ``dt = softplus(dt + dt_bias)``, ``S = exp(-exp(a_log) dt) S + dt B x^T``, ``y = S^T C + d_skip x``.  ``xbc [tokens, heads
+    * vdim + 2 * groups * n_state]`` holds x, B and C; ``dt [tokens, heads]`` (rows of both may be strided); ``y`` float32
+    ``[tokens, heads * vdim]``.  A request's state (``[heads, vdim, n_state]``, the first entries of its slot of ``state``) is
+    read at the start and written back at the end; slot -1: zero, not written."""
+    need_cuda(xbc, dt, dt_bias, a_log, d_skip, state, slots, bounds, y)
+    need_int32("slots", slots)
+    need_contiguous("y", y)
+    n = xbc.shape[0]
+    inner = heads * vdim
+    if (xbc.stride(1) != 1 or dt.stride(1) != 1 or xbc.shape[1] != inner + 2 * groups * n_state or dt.shape != (n, heads) or dt.dtype != xbc.dtype
+            or y.dtype != torch.float32 or y.shape != (n, inner) or not (dt_bias.dtype == a_log.dtype == d_skip.dtype)
+            or dt_bias.numel() != heads or a_log.numel() != heads or d_skip.numel() != heads):
+        raise KernelError(f"ssm_scan: xbc {tuple(xbc.shape)}, dt {tuple(dt.shape)}, y {tuple(y.shape)} do not agree")
+    if state.shape[1] < inner * n_state:
+        raise KernelError("ssm_scan: the state slots are too small")
+    sp, ss = _state_args(state, 0)
+    _ssm.call("zi_ssm_scan", ptr(xbc), c_int(dtype_code(xbc.dtype)), c_ll(xbc.stride(0)), ptr(dt), c_ll(dt.stride(0)), ptr(dt_bias),
+              ptr(a_log), ptr(d_skip), c_int(dtype_code(dt_bias.dtype)), sp, ss, ptr(slots), ptr(bounds), ptr(y), c_int(n_segments),
+              c_int(heads), c_int(vdim), c_int(n_state), c_int(groups), stream())
+
+
+def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, n_groups: int, eps: float, out: torch.Tensor) -> None:
+    """``out = unit_rms(y * silu(z)) * w`` with the root mean square taken over each of ``n_groups`` equal parts of a row;
+    ``y`` float32, ``z`` (rows may be strided) and ``out`` of the step's type."""
+    need_cuda(y, z, w, out)
+    need_contiguous("y", y), need_contiguous("w", w), need_contiguous("out", out)
+    n, inner = y.shape
+    if y.dtype != torch.float32 or z.shape != (n, inner) or z.stride(1) != 1 or out.shape != (n, inner) or out.dtype != z.dtype or w.numel() != inner:
+        raise KernelError(f"gated_group_rmsnorm: y {tuple(y.shape)}, z {tuple(z.shape)}, out {tuple(out.shape)} do not agree")
+    _ssm.call("zi_gated_group_rmsnorm", ptr(y), ptr(z), c_int(dtype_code(z.dtype)), c_ll(z.stride(0)), ptr(w), c_int(dtype_code(w.dtype)),
+              ptr(out), c_int(n), c_int(inner), c_int(n_groups), c_float(eps), stream())

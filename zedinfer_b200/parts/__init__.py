@@ -1,7 +1,7 @@
 from .base import (Block, Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding, ResidualStream,
                    StepContext, block_class, build_part, register_block, register_embedding, register_feed_forward,
                    register_head, register_mixer, register_norm, register_position, unregister)
-from . import attention, block, embedding, latent_attention, mlp, moe, rmsnorm, rope  # noqa: F401  (registers the built-in kinds)
+from . import attention, block, embedding, latent_attention, mlp, moe, rmsnorm, rope, ssm  # noqa: F401  (registers the built-in kinds)
 from .attention import AttentionMixer
 from .block import PreNormBlock
 from .embedding import LearnedPositionEmbedding, OutputHead, TokenEmbedding
@@ -9,10 +9,11 @@ from .latent_attention import LatentAttentionMixer
 from .mlp import ClampedGatedMLP, GatedMLP, SquaredReluMLP
 from .moe import RoutedExperts
 from .rmsnorm import RMSNorm
-from .rope import RotaryPosition
+from .rope import RotaryPosition, SpanRotaryPosition
+from .ssm import Mamba2Mixer
 
 __all__ = ["Block", "Embedding", "FeedForward", "Head", "Mixer", "Norm", "Part", "PositionEncoding", "ResidualStream",
            "StepContext", "block_class", "build_part", "register_block", "register_embedding",
            "register_feed_forward", "register_head", "register_mixer", "register_norm", "register_position", "unregister", "AttentionMixer", "PreNormBlock", "OutputHead",
            "TokenEmbedding", "GatedMLP", "RMSNorm", "RotaryPosition", "LearnedPositionEmbedding", "LatentAttentionMixer",
-           "ClampedGatedMLP", "SquaredReluMLP", "RoutedExperts"]
+           "ClampedGatedMLP", "SquaredReluMLP", "RoutedExperts", "SpanRotaryPosition", "Mamba2Mixer"]

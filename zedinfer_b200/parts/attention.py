@@ -10,6 +10,11 @@ src/backend/ops/self_attention/cpu/paged_attention_cpu.cpp:113-159 for the score
 
 A query at position P sees keys ``max(0, P - window + 1) .. P`` (all keys from 0 without a
 window).  Query head ``h`` reads key/value head ``h // (num_heads // num_kv_heads)``.
+
+Options beside the reference's form: ``value_from_key`` (there is no value projection: a token's value is its key as
+projected, before the position rule turns it; the cache still has two planes, turned keys and plain ones),
+``unit_sink`` (the softmax's denominator holds one more term, ``exp(0)``, that has no key and no value: ``p_j = exp(s_j) /
+(1 + sum_j' exp(s_j'))``), and ``names`` (the local tensor names by role).
 """
 from __future__ import annotations
 
@@ -34,7 +39,8 @@ class AttentionMixer(Mixer):
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, qkv_bias: bool = True, out_bias: bool = False,
-                 scale: Optional[float] = None, window: Optional[int] = None):
+                 scale: Optional[float] = None, window: Optional[int] = None, value_from_key: bool = False,
+                 unit_sink: bool = False, names: Optional[Mapping[str, str]] = None):
         if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} query heads cannot share {num_kv_heads} key/value heads")
         if head_dim <= 0 or head_dim % 16:
@@ -49,33 +55,43 @@ class AttentionMixer(Mixer):
         self.qkv_bias, self.out_bias = bool(qkv_bias), bool(out_bias)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(float(head_dim))
         self.position = build_part("position", position)
+        self.value_from_key, self.unit_sink = bool(value_from_key), bool(unit_sink)
+        if self.value_from_key and not getattr(self.position, "takes_value_from_key", False):
+            raise ValueError(f"attention: the position rule {position.kind!r} cannot append unturned keys as values")
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                      "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias"}
+        self.names.update(names or {})
         self.q_dim, self.kv_dim = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
-        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.sinks = None
 
     def cache_need(self):
         return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        h = self.hidden_size
-        specs = {"q_proj.weight": TensorSpec((self.q_dim, h)), "k_proj.weight": TensorSpec((self.kv_dim, h)),
-                 "v_proj.weight": TensorSpec((self.kv_dim, h)), "o_proj.weight": TensorSpec((h, self.q_dim))}
+        h, nm = self.hidden_size, self.names
+        roles = ("q", "k") if self.value_from_key else ("q", "k", "v")
+        specs = {nm[r]: TensorSpec((self.q_dim if r == "q" else self.kv_dim, h)) for r in roles}
+        specs[nm["o"]] = TensorSpec((h, self.q_dim))
         if self.qkv_bias:
-            specs.update({"q_proj.bias": TensorSpec((self.q_dim,)), "k_proj.bias": TensorSpec((self.kv_dim,)),
-                          "v_proj.bias": TensorSpec((self.kv_dim,))})
+            specs.update({nm[r + "_bias"]: TensorSpec((self.q_dim if r == "q" else self.kv_dim,)) for r in roles})
         if self.out_bias:
-            specs["o_proj.bias"] = TensorSpec((h,))
+            specs[nm["o_bias"]] = TensorSpec((h,))
         return specs
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.w_qkv = _stack([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]])
+        nm = self.names
+        roles = ("q", "k") if self.value_from_key else ("q", "k", "v")
+        self.w_qkv = _stack([tensors[nm[r]] for r in roles])
         if self.qkv_bias:
-            self.b_qkv = _stack([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]])
+            self.b_qkv = _stack([tensors[nm[r + "_bias"]] for r in roles])
             if self.b_qkv.dtype != self.w_qkv.dtype:
                 # one product, one operand type: float32 wins
                 self.w_qkv, self.b_qkv = self.w_qkv.float(), self.b_qkv.float()
-        self.w_o = tensors["o_proj.weight"].contiguous()
+        self.w_o = tensors[nm["o"]].contiguous()
         if self.out_bias:
-            self.b_o = tensors["o_proj.bias"].contiguous()
+            self.b_o = tensors[nm["o_bias"]].contiguous()
+        if self.unit_sink:
+            self.sinks = torch.zeros(self.num_heads, dtype=torch.float32, device=self.w_o.device)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> torch.Tensor:
         out = ctx.empty(x.shape[0], self.hidden_size)
@@ -92,12 +108,18 @@ class AttentionMixer(Mixer):
             raise RuntimeError("attention needs a paged key/value cache")
         n = x.shape[0]
         q = ctx.empty(n, self.num_heads, self.head_dim)
-        if not self.position.project_rotate_append(x, self.w_qkv, self.b_qkv, q, cache, ctx, self.num_heads,
-                                                   self.num_kv_heads, self.head_dim, write_kv=owns_cache):
+        if self.value_from_key:
+            qk = ctx.empty(n, self.q_dim + self.kv_dim)
+            ops.linear(x, self.w_qkv, self.b_qkv, qk)
+            self.position.rotate_append(qk, q, cache, ctx, self.num_heads, self.num_kv_heads, self.head_dim,
+                                        write_kv=owns_cache, value_from_key=True)
+        elif not self.position.project_rotate_append(x, self.w_qkv, self.b_qkv, q, cache, ctx, self.num_heads,
+                                                     self.num_kv_heads, self.head_dim, write_kv=owns_cache):
             qkv = ctx.empty(n, self.q_dim + 2 * self.kv_dim)
             ops.linear(x, self.w_qkv, self.b_qkv, qkv)
             self.position.rotate_append(qkv, q, cache, ctx, self.num_heads, self.num_kv_heads, self.head_dim,
                                         write_kv=owns_cache)
         attn = ctx.empty(n, self.q_dim)
-        ops.attention(q, cache, attn, ctx, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale)
+        ops.attention(q, cache, attn, ctx, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
+                      sinks=self.sinks)
         return attn

@@ -5,7 +5,13 @@ shared one that every token runs.
     S = the ``top`` largest z        (lowest index wins a tie)
     y = sum_{e in S} softmax_S(z)_e * expert_e(x)   (+ shared(x))
 
-Each expert has the form of :class:`~zedinfer_b200.parts.mlp.ClampedGatedMLP`.  Nothing goes to the host: the step's
+Each expert has the form of :class:`~zedinfer_b200.parts.mlp.ClampedGatedMLP` (``activation="clamped_gate"``), or, with
+``activation="relu2"``, of :class:`~zedinfer_b200.parts.mlp.SquaredReluMLP`: ``down(max(up x, 0)^2)``, no gate matrix.
+``score="sigmoid"``: a chosen expert's weight is its own ``sigmoid(z_e)``, not renormalised (the choice is still by the
+largest z, which is the largest score).  ``weight_on="input"``: the weight multiplies the expert's input instead of its
+output, ``y = sum_e expert_e(w_e x)``, the scaled row rounded to the step's type before the first product.
+
+Nothing goes to the host: the step's
 (token, choice) pairs are grouped by expert on the device, the two products run as grouped products over the sorted
 rows (``csrc/moe.cu``, or the tcgen05 grouped product from a few hundred rows; the activation in the first one's epilogue), and one kernel adds a token's rows with its router
 weights and the shared expert's output in float32.
@@ -24,11 +30,20 @@ from .base import FeedForward, StepContext, build_part, register_feed_forward
 
 @register_feed_forward("routed_experts")
 class RoutedExperts(FeedForward):
-    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, limit: Optional[float],
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, limit: Optional[float] = None,
                  slope: float = 1.0, up_offset: float = 0.0, router_bias: bool = True, shared: Optional[PartSpec] = None,
                  expert_prefix: str = "e{e}.", router_name: str = "router", router_bias_name: str = "router.b",
-                 shared_prefix: str = "shared.", gate_name: str = "gate", up_name: str = "up", down_name: str = "down"):
+                 shared_prefix: str = "shared.", gate_name: str = "gate", up_name: str = "up", down_name: str = "down",
+                 activation: str = "clamped_gate", score: str = "softmax_chosen", weight_on: str = "output"):
         """``shared``: the spec of a feed-forward that every token runs as well (its tensors under ``shared_prefix``)."""
+        if activation not in ("clamped_gate", "relu2"):
+            raise ValueError(f"routed_experts: activation={activation!r} is not 'clamped_gate' or 'relu2'")
+        if score not in ops.ROUTER_SCORES:
+            raise ValueError(f"routed_experts: score={score!r} is not one of {sorted(ops.ROUTER_SCORES)}")
+        if weight_on not in ("output", "input"):
+            raise ValueError(f"routed_experts: weight_on={weight_on!r} is not 'output' or 'input'")
+        self.activation, self.score, self.weight_on = activation, score, weight_on
+        self.gated = activation == "clamped_gate"
         if hidden_size <= 0 or intermediate_size <= 0:
             raise ValueError("routed_experts: sizes must be positive")
         if experts <= 0 or experts > 1024 or not 0 < top <= experts:
@@ -54,7 +69,8 @@ class RoutedExperts(FeedForward):
             specs[self.router_bias_name] = TensorSpec((self.experts,))
         for e in range(self.experts):
             p = self.expert_prefix.format(e=e)
-            specs[p + self.gate_name] = TensorSpec((i, h))
+            if self.gated:
+                specs[p + self.gate_name] = TensorSpec((i, h))
             specs[p + self.up_name] = TensorSpec((i, h))
             specs[p + self.down_name] = TensorSpec((h, i))
         if self.shared is not None:
@@ -66,11 +82,12 @@ class RoutedExperts(FeedForward):
         self.w_router = tensors[self.router_name].contiguous()
         self.b_router = tensors[self.router_bias_name].float().contiguous() if self.router_bias else None
         names = [self.expert_prefix.format(e=e) for e in range(self.experts)]
+        first = (self.gate_name, self.up_name) if self.gated else (self.up_name,)
         dtype = torch.float32 if any(tensors[p + n].dtype == torch.float32 for p in names
-                                     for n in (self.gate_name, self.up_name, self.down_name)) else tensors[names[0] + self.gate_name].dtype
-        # [experts, 2 * inner, hidden]: an expert's gate rows, then its up rows; [experts, hidden, inner]
-        self.w_gate_up = torch.stack([torch.cat([tensors[p + self.gate_name].to(dtype), tensors[p + self.up_name].to(dtype)], dim=0)
-                                      for p in names]).contiguous()
+                                     for n in first + (self.down_name,)) else tensors[names[0] + self.up_name].dtype
+        # [experts, 2 * inner, hidden]: an expert's gate rows, then its up rows (without a gate: [experts, inner, hidden],
+        # the up rows alone); [experts, hidden, inner]
+        self.w_gate_up = torch.stack([torch.cat([tensors[p + n].to(dtype) for n in first], dim=0) for p in names]).contiguous()
         self.w_down = torch.stack([tensors[p + self.down_name].to(dtype) for p in names]).contiguous()
         if self.shared is not None:
             n = len(self.shared_prefix)
@@ -81,8 +98,12 @@ class RoutedExperts(FeedForward):
         n = x.shape[0]
         idx = torch.empty((n, self.top), dtype=torch.int32, device=x.device)
         wts = torch.empty((n, self.top), dtype=torch.float32, device=x.device)
-        ops.route(x, self.w_router, self.b_router, self.top, idx, wts)    # float32 logits whatever the operands' type
+        ops.route(x, self.w_router, self.b_router, self.top, idx, wts, score=self.score)    # float32 logits whatever the operands' type
         return idx, wts
+
+    def _first_product(self) -> dict:
+        """The activation of the experts' first product, as the grouped products' keywords."""
+        return {"gated": (self.limit, self.slope, self.up_offset)} if self.gated else {"relu2": True}
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         n, pairs = x.shape[0], x.shape[0] * self.top
@@ -94,12 +115,13 @@ class RoutedExperts(FeedForward):
         pair_row = torch.empty(pairs, dtype=torch.int32, device=x.device)
         ops.moe_group(idx, self.experts, offsets, row_pair, pair_row)
         act = ctx.empty(pairs, self.intermediate_size)
-        ops.moe_gemm(x, row_pair, self.top, self.w_gate_up, offsets, act, gated=(self.limit, self.slope, self.up_offset))
+        on_input = self.weight_on == "input"
+        ops.moe_gemm(x, row_pair, self.top, self.w_gate_up, offsets, act, a_scale=wts if on_input else None, **self._first_product())
         y = ctx.empty(pairs, self.hidden_size)
         ops.moe_gemm(act, None, 1, self.w_down, offsets, y)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         out = ctx.empty(n, self.hidden_size)
-        ops.moe_combine(y, pair_row, wts, shared, out)
+        ops.moe_combine(y, pair_row.view(n, self.top), None if on_input else wts, shared, out)
         return out
 
     def _tcgen05_ok(self, x: torch.Tensor, pairs: int) -> bool:
@@ -119,12 +141,13 @@ class RoutedExperts(FeedForward):
         tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
         ops.moe_group_padded(idx, self.experts, pad, starts, row_pair, pair_row, tile_expert)
         xs = ctx.empty(tiles * pad, self.hidden_size)
-        ops.moe_gather_rows(x, row_pair, self.top, xs)
+        on_input = self.weight_on == "input"
+        ops.moe_gather_rows(x, row_pair, self.top, xs, scale=wts if on_input else None)
         act = ctx.empty(tiles * pad, self.intermediate_size)
-        ops.gemm_tcgen05_grouped(xs, self.w_gate_up, tile_expert, act, gated=(self.limit, self.slope, self.up_offset))
+        ops.gemm_tcgen05_grouped(xs, self.w_gate_up, tile_expert, act, **self._first_product())
         y = ctx.empty(tiles * pad, self.hidden_size)
         ops.gemm_tcgen05_grouped(act, self.w_down, tile_expert, y)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         out = ctx.empty(n, self.hidden_size)
-        ops.moe_combine(y, pair_row, wts, shared, out)
+        ops.moe_combine(y, pair_row.view(n, self.top), None if on_input else wts, shared, out)
         return out

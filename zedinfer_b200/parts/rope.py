@@ -1,4 +1,7 @@
-"""Rotate-half rotary position encoding over the whole head.
+"""Rotary position encodings: rotate-half over the whole head (``rope``), and a span of the head in either pairing
+(``rope_span``).
+
+``rope``:
 
 ``inv_freq[k] = 1 / theta^(2k / head_dim)`` in float32, ``angle = float(position) * inv_freq[k]``,
 ``y[k] = a*cos - b*sin``, ``y[k + half] = b*cos + a*sin`` with ``a = x[k]``, ``b = x[k + half]``
@@ -74,3 +77,49 @@ class RotaryPosition(PositionEncoding):
                              ctx.positions, n_heads, n_kv_heads, head_dim, cache.page_size, cache.page_stride,
                              cache.kv_stride)
         return True
+
+
+@register_position("rope_span")
+class SpanRotaryPosition(PositionEncoding):
+    """Only entries ``offset .. offset + dims`` of a head turn, the rest pass unchanged.  Pair i of the span is (entry i,
+    entry i + dims / 2) (``interleaved=False``, the rotate-half pairing) or (entry 2i, entry 2i + 1) (``interleaved=True``);
+    ``(lo, hi) -> (lo cos a - hi sin a, hi cos a + lo sin a)`` with ``a = float(position) * inv_freq[i]``, ``inv_freq[i] =
+    1 / theta^(2i / dims)`` in float32.  The kernel that turns also appends the keys and the values to the cache; with
+    ``value_from_key`` the values are the keys as they were before the turn (the product then has no value columns)."""
+    capture_safe = True
+    takes_value_from_key = True
+
+    def __init__(self, head_dim: int, dims: int, theta: float, interleaved: bool = False, offset: int = 0):
+        if head_dim <= 0 or dims <= 0 or dims % 2 or offset < 0 or offset + dims > head_dim:
+            raise ValueError(f"rope_span: a span of {dims} entries from {offset} must be even and fit a head of {head_dim}")
+        if not theta > 0.0:
+            raise ValueError(f"rope_span: theta={theta} must be positive")
+        self.head_dim, self.dims, self.theta = int(head_dim), int(dims), float(theta)
+        self.interleaved, self.offset = bool(interleaved), int(offset)
+        self._inv_freq: Optional[torch.Tensor] = None
+
+    def inverse_frequencies(self) -> torch.Tensor:
+        """float32 table on the CPU: 1 / powf(theta, float(2i) / float(dims))."""
+        expo = torch.arange(0, self.dims, 2, dtype=torch.float32) / torch.tensor(float(self.dims), dtype=torch.float32)
+        return 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float32), expo)
+
+    def table(self, device: torch.device) -> torch.Tensor:
+        if self._inv_freq is None or self._inv_freq.device != device:
+            self._inv_freq = self.inverse_frequencies().to(device)
+        return self._inv_freq
+
+    def rotate_append(self, qkv: torch.Tensor, q_out: torch.Tensor, cache: CallCacheView, ctx: StepContext,
+                      n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool, value_from_key: bool = False) -> None:
+        if head_dim != self.head_dim:
+            raise ValueError(f"rope_span was built for head_dim={self.head_dim}, the mixer has {head_dim}")
+        if not write_kv:
+            ops.rotary(qkv, q_out, ctx.positions, self.table(qkv.device), n_heads, 0, head_dim, self.offset, self.dims,
+                       self.interleaved)
+            return
+        ops.rotary(qkv, q_out, ctx.positions, self.table(qkv.device), n_heads, n_kv_heads, head_dim, self.offset, self.dims,
+                   self.interleaved, cache=cache, tables=ctx.tables[cache.group], tok_seg=ctx.tok_seg,
+                   v_mode=2 if value_from_key else 1)
+
+    def rotate_queries(self, q: torch.Tensor, ctx: StepContext, n_heads: int) -> None:
+        """In place, queries alone: ``q [tokens, n_heads * head_dim]`` (rows may be strided)."""
+        ops.rotary(q, q, ctx.positions, self.table(q.device), n_heads, 0, self.head_dim, self.offset, self.dims, self.interleaved)
