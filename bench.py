@@ -330,6 +330,25 @@ DESIGN_SIZES = {
 }
 
 
+def gibalorn_config(width, heads, layers, vocab, experts, top, expert_ff, dim=128, **_):
+    """The Gibalorn design at the same width, layers, heads, head size, vocabulary and experts: its three mixers in turn
+    (state-space, latent attention, attention, latent attention), a routed feed-forward in every layer (the design has no
+    dense one and no shared expert).  State-space layers of twice the width in heads of 64 columns with a state of 128;
+    latent rows of 64 + 64 entries, queries through a latent of a quarter of the width; half of every head turned."""
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    rot = {"base": 10000.0, "dims": dim // 2}
+    kinds = [
+        {"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}},
+        {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "kv_rank": dim // 2,
+                                               "q_rank": width // 4, "scale": (dim + dim // 2) ** -0.5, "rot": rot}},
+        {"type": "attention", "mixer": {"heads": heads, "kv_heads": 2 if heads <= 12 else 4, "dim": dim, "vdim": dim,
+                                        "scale": dim ** -0.5, "rot": rot}},
+    ]
+    out = [dict(kinds[(0, 1, 2, 1)[i % 4]], mlp=moe) for i in range(layers)]
+    return {"architecture": "Gibalorn", "vocab": vocab, "width": width, "max_positions": CONTEXT, "norm": {"eps": 1e-6},
+            "layers": out, "loop": None}
+
+
 def measure_design(cfg, vocab, batch, steps, warmup):
     """Prefill of PROMPT_LEN tokens in one step and decode of `batch` requests through the captured greedy step."""
     import torch
@@ -379,7 +398,7 @@ def design_comparison(args):
     import torch  # noqa: F401
     from zedinfer_b200.csrc import build
     from zedinfer_b200.engine.core import EngineCore
-    build.compile_all(EngineCore.kernel_libraries("bfloat16") + ["gemm_tcgen05", "attention_tcgen05", "rowwise", "moe"], verbose=False)
+    build.compile_all(EngineCore.kernel_libraries("bfloat16") + ["gemm_tcgen05", "attention_tcgen05", "rowwise", "moe", "ssm"], verbose=False)
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     clocks = ClockSampler()
     clocks.start()
@@ -388,9 +407,16 @@ def design_comparison(args):
         q = {k: size[k] for k in ("width", "heads", "ff", "window", "layers", "vocab")}
         base = measure_design(baselix_config(**size), size["vocab"], args.batch, steps, warmup)
         qwen = measure_design(qwen2_config_like(**q), size["vocab"], args.batch, steps, warmup)
-        rows.append({"size": name, "shape": size, "baselix": base, "qwen2_equal_size": qwen,
-                     "prefill_ratio": round(base["prefill_tokens_per_s"] / qwen["prefill_tokens_per_s"], 3),
-                     "decode_ratio": round(base["decode_tokens_per_s"] / qwen["decode_tokens_per_s"], 3)})
+        row = {"size": name, "shape": size, "baselix": base, "qwen2_equal_size": qwen,
+               "prefill_ratio": round(base["prefill_tokens_per_s"] / qwen["prefill_tokens_per_s"], 3),
+               "decode_ratio": round(base["decode_tokens_per_s"] / qwen["decode_tokens_per_s"], 3)}
+        if args.designs == "gibalorn":
+            # the new design beside its closest relative (latent attention and routed experts) and beside Qwen2
+            gib = measure_design(gibalorn_config(**size), size["vocab"], args.batch, steps, warmup)
+            row.update({"gibalorn": gib,
+                        "gibalorn_prefill_ratio_to_baselix": round(gib["prefill_tokens_per_s"] / base["prefill_tokens_per_s"], 3),
+                        "gibalorn_decode_ratio_to_baselix": round(gib["decode_tokens_per_s"] / base["decode_tokens_per_s"], 3)})
+        rows.append(row)
     clocks.stop()
     print(json.dumps({"metric": "designs_side_by_side", "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
                       "dtype": "bf16", "data": "synthetic", "impl": "ours", "batch": args.batch, "prompt_len": PROMPT_LEN,
@@ -485,9 +511,10 @@ def main():
     ap.add_argument("--layers", type=int, default=MODEL_1P5B["num_hidden_layers"],
                     help="fewer layers than the model has (same layer sizes), where memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
-    ap.add_argument("--designs", action="store_true",
+    ap.add_argument("--designs", nargs="?", const="baselix", default=None, choices=["baselix", "gibalorn"],
                     help="instead of the default workload: prefill and decode of the Baselix design at layer sizes of real "
-                         "models (random weights) beside Qwen2 at equal size")
+                         "models (random weights) beside Qwen2 at equal size; '--designs gibalorn' also runs the Gibalorn "
+                         "design at those sizes")
     args = ap.parse_args()
 
     if args.impl == "reference":

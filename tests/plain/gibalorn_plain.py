@@ -199,6 +199,15 @@ def route(h: torch.Tensor, w_router: torch.Tensor, top: int):
     return order, torch.gather(s, 1, order)
 
 
+def route_margin(h: torch.Tensor, w_router: torch.Tensor, top: int) -> torch.Tensor:
+    """Per token, how far the last chosen expert's logit lies above the first one left out (infinite when all are chosen):
+    a choice with a small margin is a close call that rounding may turn the other way."""
+    z = torch.sort(h @ w_router.T, dim=-1, descending=True).values
+    if top >= z.shape[1]:
+        return torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+    return z[:, top - 1] - z[:, top]
+
+
 def routed_feed_forward(h: torch.Tensor, f: dict, w: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
     idx, wts = route(h, w[p + "router"], f["router"]["top"])
     out = torch.zeros_like(h)
@@ -222,8 +231,10 @@ def run_order(cfg: dict) -> List[int]:
     return list(range(a)) + list(range(a, b)) * r + list(range(b, n))
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], layer_outputs: Optional[list] = None) -> torch.Tensor:
-    """Logits ``[T, vocab]`` of every position of one sequence."""
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], layer_outputs: Optional[list] = None,
+            margins: Optional[list] = None) -> torch.Tensor:
+    """Logits ``[T, vocab]`` of every position of one sequence.  ``layer_outputs`` receives the residual stream after every
+    layer run, ``margins`` the router's margin per token (:func:`route_margin`) of every routed layer run."""
     eps = cfg["norm"]["eps"]
     dtype = w["embed"].dtype
     positions = torch.arange(len(tokens))
@@ -252,6 +263,18 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], layer_outp
         if layer.get("mlp") is not None:
             h = rms_norm(x, w[f"l{i}.norm2"], eps)
             x = x + routed_feed_forward(h, layer["mlp"], w, f"l{i}.mlp.")
+            if margins is not None:
+                margins.append(route_margin(h, w[f"l{i}.mlp.router"], layer["mlp"]["router"]["top"]))
         if layer_outputs is not None:
             layer_outputs.append(x.clone())
     return rms_norm(x, w["final.norm"], eps).to(dtype) @ w["head"].T
+
+
+def greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    """``n_new`` tokens, each the most likely one (the lowest index among equals), the whole sequence run again each time."""
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        tok = int(torch.argmax(forward(cfg, w, seq)[-1]))
+        out.append(tok)
+        seq.append(tok)
+    return out
