@@ -214,6 +214,36 @@ def test_the_scan_carries_its_state_from_step_to_step(dtype, heads, vdim, n_stat
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,vdim,n_state,groups", [(2, 64, 128, 1), (3, 12, 8, 3), (2, 20, 40, 2)])
+def test_long_portions_in_stretches_side_by_side_equal_the_plain_walk(dtype, heads, vdim, n_state, groups):
+    """Segments of 1, 127, 128, 129 and 700 tokens in one step, one of them continuing from a state that an earlier step
+    left and one a row of padding: cut into stretches that run side by side, the outputs and the states left behind agree
+    with the plain walk of every segment to float32 rounding."""
+    from zedinfer_b200 import ops
+    g = torch.Generator().manual_seed(n_state)
+    inner, width = heads * vdim, heads * vdim + 2 * groups * n_state
+    lens = [1, 127, 128, 129, 700, 1]
+    slots = torch.tensor([3, 0, 5, 1, 2, -1], dtype=torch.int32, device=DEV)
+    n = sum(lens)
+    xbc = (torch.randn(n, width, generator=g) * 0.5).to(dtype).to(DEV)
+    dt = torch.randn(n, heads, generator=g).to(dtype).to(DEV)
+    par = [t.to(DEV) for t in (torch.randn(heads, generator=g) - 1.0, torch.randn(heads, generator=g) * 0.5, torch.randn(heads, generator=g))]
+    tok_seg = torch.tensor([i for i, k in enumerate(lens) for _ in range(k)], dtype=torch.int32, device=DEV)
+    bounds = torch.empty(len(lens), 2, dtype=torch.int32, device=DEV)
+    ops.segment_bounds(tok_seg, len(lens), bounds)
+    start = torch.randn(6, inner * n_state + 3, generator=g).to(DEV)
+    out, left = [], []
+    for stretchwise in (False, True):
+        state = start.clone()
+        y = torch.empty(n, inner, dtype=torch.float32, device=DEV)
+        ops.ssm_scan(xbc, dt, *par, state, slots, bounds, y, len(lens), heads, vdim, n_state, groups, stretchwise=stretchwise)
+        out.append(y.cpu())
+        left.append(state.cpu())
+    assert rel_err(out[1], out[0].double()) < 2e-5 and rel_err(left[1], left[0].double()) < 2e-5
+    assert torch.equal(left[1][4], start[4].cpu()) and torch.equal(left[1][:, inner * n_state:], start[:, inner * n_state:].cpu())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("inner,parts", [(48, 1), (96, 3), (1200, 2), (20, 20)])
 def test_gate_then_norm_in_equal_parts(dtype, inner, parts):
     from zedinfer_b200 import ops

@@ -109,56 +109,163 @@ ZI_EXPORT int zi_conv_state_update(const void* u, int dtype, long long ldu, floa
 
 // ---------------------------------------------------------------------------------------
 // The scan.  A block takes (segment, head, a tile of the head's columns p) and walks the segment's tokens in order.
-// A column's state entries are dealt to L lanes of a warp (L a power of two, R = ceil(N / L) <= 16 entries each, lane l
-// holding n = l R .. l R + R - 1), so a warp holds 32 / L columns.  Tokens come in chunks: B, C, x, the step sizes and
-// the decays of a chunk are put into shared memory by the whole block, then every thread walks the chunk.
+// A column's state entries are dealt in blocks of R4 (4, 8 or 16) to L lanes of a warp (L a power of two, L * R4 >= N);
+// a thread holds the blocks of CPT (1 or 4) neighbouring columns, so that what it reads of B and C serves all of them:
+// per token 2 * R4 values from shared memory (16-byte loads; a lane's block starts R4 + 4 floats after its neighbour's, so
+// that the eight lanes of a quarter warp hit different banks) against 3 * CPT * R4 multiply-adds.  Tokens come in
+// chunks: B, C, x, the step sizes and the decays of a chunk are put into shared memory by the whole block, then every
+// thread walks the chunk.  A column's sum over the lanes: with four columns per thread the lanes first halve what they
+// hold twice (two exchanges, then one), so that four lanes end with one column each, then add across the rest.
+// State in memory: [heads, vdim, N], a column's entries consecutive.
 // ---------------------------------------------------------------------------------------
-#define SCAN_R 16
-#define SCAN_CHUNK 32
+#define SCAN_CHUNK 16
+// Long portions (bfloat16 steps): a segment is cut into stretches of SCAN_STRETCH tokens that run side by side.
+//   MODE 1  every stretch from a zero state: its own end state and the product of its decays go to a scratch buffer
+//   (zi_ssm_combine)  a segment's stretches in order: start state of stretch k = what the request's slot held, carried
+//           through stretches 0 .. k-1; it replaces the stretch's own end state in the scratch buffer; the slot receives
+//           the state behind the last stretch
+//   MODE 2  every stretch again from its start state, this time with C and the outputs
+// MODE 0 is the plain walk of a whole segment from the slot's state (float32 steps, short portions, decode steps): its
+// sums have one order whatever the cut.  The stretches' sums are the same sums in another order.
+#define SCAN_STRETCH 128
 
 __device__ __forceinline__ float softplus_f32(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
 
-template <typename T, typename TP>
+// Which (segment, tokens) a block of a stretch-wise launch works on: stretch number `id` counted through the segments.
+__device__ __forceinline__ bool find_stretch(const int* __restrict__ bounds, int n_segments, int id, int* seg, int* first, int* end) {
+    for (int s = 0; s < n_segments; ++s) {
+        const int b = bounds[2 * s], e = bounds[2 * s + 1];
+        const int k = (e - b + SCAN_STRETCH - 1) / SCAN_STRETCH;
+        if (id < k) {
+            *seg = s;
+            *first = b + id * SCAN_STRETCH;
+            *end = *first + SCAN_STRETCH < e ? *first + SCAN_STRETCH : e;
+            return true;
+        }
+        id -= k;
+    }
+    return false;
+}
+
+template <typename T, typename TP, int R4, int CPT, int MODE>
 __global__ void __launch_bounds__(256)
 ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ dt_in, long long ld_dt,
                 const TP* __restrict__ dt_bias, const TP* __restrict__ a_log, const TP* __restrict__ d_skip,
                 float* __restrict__ state, long long slot_stride, const int* __restrict__ slots,
-                const int* __restrict__ bounds, float* __restrict__ y, int heads, int vdim, int N, int groups,
-                int L, int R, int chunk) {
-    extern __shared__ float sm[];
-    const int seg = blockIdx.x, h = blockIdx.y;
-    const int warps = blockDim.x >> 5, pt = 32 / L, pc = warps * pt;
+                const int* __restrict__ bounds, float* __restrict__ y, int heads, int vdim, int N, int groups, int L,
+                int n_segments, float* __restrict__ scratch, float* __restrict__ decay_out) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int RS = R4 == 4 ? 4 : R4 + 4;          // floats between the blocks of neighbouring lanes
+    const int h = blockIdx.y;
+    const int warps = blockDim.x >> 5, cpw = (32 / L) * CPT, pc = warps * cpw;       // columns per warp, per block
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nl = lane % L, col = warp * pt + lane / L;
-    const int p = blockIdx.z * pc + col;
+    const int nl = lane % L, col = warp * cpw + (lane / L) * CPT;                    // first of the thread's columns in the tile
+    const int p0 = blockIdx.z * pc + col;
     const int g = h / (heads / groups);
     const int inner = heads * vdim;
-    const int first = bounds ? bounds[2 * seg] : seg, end = bounds ? bounds[2 * seg + 1] : seg + 1;
-    const int slot = slots[seg];
-    float* Bs = sm;                         // [chunk][N]
-    float* Cs = Bs + (size_t)chunk * N;     // [chunk][N]
-    float* xs = Cs + (size_t)chunk * N;     // [chunk][pc]
-    float* dts = xs + (size_t)chunk * pc;   // [chunk]
-    float* decs = dts + chunk;              // [chunk]
+    const int row = L * RS;
+    int seg = blockIdx.x, first, end;
+    if (MODE == 0) {
+        first = bounds ? bounds[2 * seg] : seg;
+        end = bounds ? bounds[2 * seg + 1] : seg + 1;
+    } else if (!find_stretch(bounds, n_segments, blockIdx.x, &seg, &first, &end)) {
+        return;
+    }
+    float* Bs = sm;                                  // [chunk][row]
+    float* Cs = Bs + SCAN_CHUNK * row;               // [chunk][row]
+    float* xs = Cs + SCAN_CHUNK * row;               // [chunk][pc]
+    float* dts = xs + SCAN_CHUNK * pc;               // [chunk]
+    float* decs = dts + SCAN_CHUNK;                  // [chunk]
+    for (int i = threadIdx.x; i < 2 * SCAN_CHUNK * row; i += blockDim.x) sm[i] = 0.0f;     // entries beyond N stay zero
     const float a_rate = expf(to_f32<TP>(a_log[h])), bias = to_f32<TP>(dt_bias[h]), skip = to_f32<TP>(d_skip[h]);
-    const bool live = p < vdim;
-    float S[SCAN_R];
-    float* srow = (slot >= 0 && live) ? state + (size_t)slot * slot_stride + ((size_t)h * vdim + p) * N + (size_t)nl * R : nullptr;
+    float S[CPT][R4];
+    // where this block's state comes from and goes to: the request's slot, or the stretch's place in the scratch buffer
+    float* sbase;
+    bool vec;
+    if (MODE == 0) {
+        const int slot = slots[seg];
+        sbase = slot >= 0 ? state + (size_t)slot * slot_stride + (size_t)h * vdim * N : nullptr;
+        vec = (N & 3) == 0 && (slot_stride & 3) == 0 && ((uintptr_t)state & 15) == 0;
+    } else {
+        sbase = scratch + ((size_t)blockIdx.x * heads + h) * vdim * N;
+        vec = (N & 3) == 0 && ((uintptr_t)scratch & 15) == 0;
+    }
 #pragma unroll
-    for (int r = 0; r < SCAN_R; ++r) S[r] = (srow && r < R && nl * R + r < N) ? srow[r] : 0.0f;
-    for (int t0 = first; t0 < end; t0 += chunk) {
-        const int cnt = end - t0 < chunk ? end - t0 : chunk;
-        __syncthreads();
-        for (int i = threadIdx.x; i < cnt * N; i += blockDim.x) {
-            const int t = i / N, n = i - t * N;
-            const T* row = xbc + (size_t)(t0 + t) * ldx + inner + (size_t)g * N + n;
-            Bs[i] = to_f32<T>(row[0]);
-            Cs[i] = to_f32<T>(row[(size_t)groups * N]);
+    for (int c = 0; c < CPT; ++c) {
+        const bool live = MODE != 1 && sbase && p0 + c < vdim;
+        const float* src = live ? sbase + (size_t)(p0 + c) * N + nl * R4 : nullptr;
+#pragma unroll
+        for (int r = 0; r < R4; r += 4) {
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (live) {
+                if (vec) {
+                    if (nl * R4 + r < N) v = *reinterpret_cast<const float4*>(src + r);
+                } else {
+                    if (nl * R4 + r + 0 < N) v.x = src[r + 0];
+                    if (nl * R4 + r + 1 < N) v.y = src[r + 1];
+                    if (nl * R4 + r + 2 < N) v.z = src[r + 2];
+                    if (nl * R4 + r + 3 < N) v.w = src[r + 3];
+                }
+            }
+            S[c][r] = v.x; S[c][r + 1] = v.y; S[c][r + 2] = v.z; S[c][r + 3] = v.w;
         }
-        for (int i = threadIdx.x; i < cnt * pc; i += blockDim.x) {
-            const int t = i / pc, c = i - t * pc;
-            const int pp = blockIdx.z * pc + c;
-            xs[i] = pp < vdim ? to_f32<T>(xbc[(size_t)(t0 + t) * ldx + (size_t)h * vdim + pp]) : 0.0f;
+    }
+    // eight values per load where everything is a multiple of eight and aligned for it
+    const bool vec8 = (N & 7) == 0 && (pc & 7) == 0 && (vdim & 7) == 0 && (inner & 7) == 0 && (ldx & 7) == 0 &&
+                      ((uintptr_t)xbc % (8 * sizeof(T))) == 0;
+    float decay_all = 1.0f;
+    for (int t0 = first; t0 < end; t0 += SCAN_CHUNK) {
+        const int cnt = end - t0 < SCAN_CHUNK ? end - t0 : SCAN_CHUNK;
+        __syncthreads();
+        if (vec8) {
+            // per token: N / 8 pieces of B, as many of C (MODE 1 needs none), pc / 8 of x; all of a round's loads before its stores
+            const int nb = N >> 3, per = (MODE == 1 ? nb : 2 * nb) + (pc >> 3), items = cnt * per;
+            for (int i0 = threadIdx.x; i0 < items; i0 += 4 * blockDim.x) {
+                float v[4][8];
+                int at[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int i = i0 + q * blockDim.x;
+                    at[q] = -1;
+                    if (i < items) {
+                        const int t = i / per, k = i - t * per;
+                        const T* rowp = xbc + (size_t)(t0 + t) * ldx;
+                        if (k < nb) {
+                            load8(rowp + inner + (size_t)g * N + k * 8, v[q]);
+                            at[q] = t * row + ((k * 8) / R4) * RS + (k * 8) % R4;
+                        } else if (MODE != 1 && k < 2 * nb) {
+                            load8(rowp + inner + (size_t)(groups + g) * N + (k - nb) * 8, v[q]);
+                            at[q] = SCAN_CHUNK * row + t * row + (((k - nb) * 8) / R4) * RS + ((k - nb) * 8) % R4;
+                        } else {
+                            const int c8 = (k - (MODE == 1 ? nb : 2 * nb)) * 8, pp = blockIdx.z * pc + c8;
+                            if (pp < vdim) load8(rowp + (size_t)h * vdim + pp, v[q]);
+                            else
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[q][e] = 0.0f;
+                            at[q] = 2 * SCAN_CHUNK * row + t * pc + c8;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (at[q] >= 0) {
+                        // eight values lie in one block of R4 = 8 or 16, or in two blocks of 4
+                        *reinterpret_cast<float4*>(sm + at[q]) = make_float4(v[q][0], v[q][1], v[q][2], v[q][3]);
+                        const int second = (R4 == 4 && at[q] < 2 * SCAN_CHUNK * row) ? at[q] + RS : at[q] + 4;
+                        *reinterpret_cast<float4*>(sm + second) = make_float4(v[q][4], v[q][5], v[q][6], v[q][7]);
+                    }
+            }
+        } else {
+            for (int t = warp; t < cnt; t += warps) {
+                const T* src = xbc + (size_t)(t0 + t) * ldx + inner + (size_t)g * N;
+                for (int n = lane; n < N; n += 32) {
+                    const int at = t * row + (n / R4) * RS + (n % R4);
+                    Bs[at] = to_f32<T>(src[n]);
+                    if (MODE != 1) Cs[at] = to_f32<T>(src[(size_t)groups * N + n]);
+                }
+                const T* xsrc = xbc + (size_t)(t0 + t) * ldx + (size_t)h * vdim + blockIdx.z * pc;
+                for (int c = lane; c < pc; c += 32) xs[t * pc + c] = blockIdx.z * pc + c < vdim ? to_f32<T>(xsrc[c]) : 0.0f;
+            }
         }
         for (int t = threadIdx.x; t < cnt; t += blockDim.x) {
             const float dt = softplus_f32(to_f32<T>(dt_in[(size_t)(t0 + t) * ld_dt + h]) + bias);
@@ -167,56 +274,185 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
         }
         __syncthreads();
         for (int t = 0; t < cnt; ++t) {
-            const float a = decs[t], xv = xs[t * pc + col], dx = dts[t] * xv;
-            const float* bt = Bs + (size_t)t * N + nl * R;
-            const float* ct = Cs + (size_t)t * N + nl * R;
-            float acc = 0.0f;
+            const float a = decs[t], dt = dts[t];
+            if (MODE == 1) decay_all *= a;
+            float xv[CPT], dx[CPT], acc[CPT];
 #pragma unroll
-            for (int r = 0; r < SCAN_R; ++r) {
-                if (r < R && nl * R + r < N) {
-                    S[r] = fmaf(dx, bt[r], a * S[r]);
-                    acc = fmaf(S[r], ct[r], acc);
+            for (int c = 0; c < CPT; ++c) { xv[c] = xs[t * pc + col + c]; dx[c] = dt * xv[c]; acc[c] = 0.0f; }
+            const float* bt = Bs + t * row + nl * RS;
+            const float* ct = Cs + t * row + nl * RS;
+#pragma unroll
+            for (int r = 0; r < R4; r += 4) {
+                const float4 b4 = *reinterpret_cast<const float4*>(bt + r);
+                const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+                if (MODE == 1) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+#pragma unroll
+                        for (int c = 0; c < CPT; ++c) S[c][r + e] = fmaf(dx[c], bv[e], a * S[c][r + e]);
+                    continue;
+                }
+                const float4 c4 = *reinterpret_cast<const float4*>(ct + r);
+                const float cv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+#pragma unroll
+                    for (int c = 0; c < CPT; ++c) {
+                        S[c][r + e] = fmaf(dx[c], bv[e], a * S[c][r + e]);
+                        acc[c] = fmaf(S[c][r + e], cv[e], acc[c]);
+                    }
+            }
+            if (MODE == 1) continue;
+            if (CPT == 4 && L >= 4) {
+                // lanes halve what they hold: after two exchanges lane (nl & 3) holds column ((nl & 1) ? 2 : 0) + ((nl & 2) ? 1 : 0);
+                // every column's sum is the same tree over the lanes as the plain exchange below makes
+                const bool hi = lane & 1, hi2 = lane & 2;
+                const float r0 = __shfl_xor_sync(0xffffffffu, hi ? acc[0] : acc[CPT > 2 ? 2 : 0], 1);
+                const float r1 = __shfl_xor_sync(0xffffffffu, hi ? acc[CPT > 1 ? 1 : 0] : acc[CPT > 3 ? 3 : 0], 1);
+                const float k0 = (hi ? acc[CPT > 2 ? 2 : 0] : acc[0]) + r0, k1 = (hi ? acc[CPT > 3 ? 3 : 0] : acc[CPT > 1 ? 1 : 0]) + r1;
+                float keep = (hi2 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, hi2 ? k0 : k1, 2);
+                for (int o = 4; o < L; o <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+                const int c = (hi ? 2 : 0) + (hi2 ? 1 : 0);
+                if (nl < 4 && p0 + c < vdim) {
+                    const float xc = c == 0 ? xv[0] : (c == 1 ? xv[CPT > 1 ? 1 : 0] : (c == 2 ? xv[CPT > 2 ? 2 : 0] : xv[CPT > 3 ? 3 : 0]));
+                    y[(size_t)(t0 + t) * inner + (size_t)h * vdim + p0 + c] = fmaf(skip, xc, keep);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                    float v = acc[c];
+                    for (int o = 1; o < L; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    if (nl == 0 && p0 + c < vdim) y[(size_t)(t0 + t) * inner + (size_t)h * vdim + p0 + c] = fmaf(skip, xv[c], v);
                 }
             }
-            for (int o = 1; o < L; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (nl == 0 && live) y[(size_t)(t0 + t) * inner + (size_t)h * vdim + p] = fmaf(skip, xv, acc);
         }
     }
-    if (srow) {
+    if (MODE == 2) return;
+    if (MODE == 1 && threadIdx.x == 0 && blockIdx.z == 0) decay_out[(size_t)blockIdx.x * heads + h] = decay_all;
 #pragma unroll
-        for (int r = 0; r < SCAN_R; ++r)
-            if (r < R && nl * R + r < N) srow[r] = S[r];
+    for (int c = 0; c < CPT; ++c) {
+        if (!(sbase && p0 + c < vdim)) continue;
+        float* dst = sbase + (size_t)(p0 + c) * N + nl * R4;
+#pragma unroll
+        for (int r = 0; r < R4; r += 4) {
+            if (vec) {
+                if (nl * R4 + r < N) *reinterpret_cast<float4*>(dst + r) = make_float4(S[c][r], S[c][r + 1], S[c][r + 2], S[c][r + 3]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (nl * R4 + r + e < N) dst[r + e] = S[c][r + e];
+            }
+        }
     }
 }
 
+// A segment's stretches in order, one thread per state entry: the start state of every stretch replaces its own end state
+// in the scratch buffer, and the slot receives the state behind the last one.
+__global__ void ssm_combine_kernel(float* __restrict__ scratch, const float* __restrict__ decay, float* __restrict__ state,
+                                   long long slot_stride, const int* __restrict__ slots, const int* __restrict__ bounds,
+                                   int n_segments, int heads, int per_head) {
+    const int seg = blockIdx.y;
+    const int slot = slots[seg];
+    int id0 = 0;
+    for (int s = 0; s < seg; ++s) id0 += (bounds[2 * s + 1] - bounds[2 * s] + SCAN_STRETCH - 1) / SCAN_STRETCH;
+    const int k = (bounds[2 * seg + 1] - bounds[2 * seg] + SCAN_STRETCH - 1) / SCAN_STRETCH;
+    const size_t all = (size_t)heads * per_head;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < all; i += (size_t)gridDim.x * blockDim.x) {
+        const int h = (int)(i / per_head);
+        float run = slot >= 0 ? state[(size_t)slot * slot_stride + i] : 0.0f;
+        // eight stretches at a time: their end states and decays are asked for together, then carried through in order
+        for (int j0 = 0; j0 < k; j0 += 8) {
+            float own[8], dec[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (j0 + q < k) {
+                    own[q] = __ldcg(scratch + (size_t)(id0 + j0 + q) * all + i);
+                    dec[q] = __ldcg(decay + (size_t)(id0 + j0 + q) * heads + h);
+                }
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (j0 + q < k) {
+                    scratch[(size_t)(id0 + j0 + q) * all + i] = run;
+                    run = fmaf(dec[q], run, own[q]);
+                }
+        }
+        if (slot >= 0 && k > 0) state[(size_t)slot * slot_stride + i] = run;
+    }
+}
+
+template <typename T, typename TP, int R4, int CPT>
+static int ssm_scan_launch(const void* xbc, long long ldx, const void* dt_in, long long ld_dt, const void* dt_bias, const void* a_log,
+                           const void* d_skip, float* state, long long slot_stride, const int* slots, const int* bounds, float* y,
+                           int n_segments, int heads, int vdim, int N, int groups, int L, int stretches, float* scratch,
+                           cudaStream_t stream) {
+    constexpr int RS = R4 == 4 ? 4 : R4 + 4;
+    const int cpw = (32 / L) * CPT;
+    int warps = (vdim + cpw - 1) / cpw;
+    if (warps > 8) warps = 8;
+    const int pc = warps * cpw;
+    const int ptiles = (vdim + pc - 1) / pc;
+    const size_t smem = (size_t)SCAN_CHUNK * (2 * L * RS + pc + 2) * sizeof(float);
+    if (heads > 65535 || ptiles > 65535) return zi_fail("ssm_scan: too many heads or columns for one launch");
+    if (smem > 200 * 1024) return zi_fail("ssm_scan: %zu bytes of shared memory", smem);
+#define ZI_SCAN_GO(MODE_, GRIDX_)                                                                                              \
+    {                                                                                                                          \
+        auto fn = ssm_scan_kernel<T, TP, R4, CPT, MODE_>;                                                                      \
+        if (smem > 48 * 1024 && cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+            return zi_fail("ssm_scan: cannot reserve %zu bytes of shared memory", smem);                                       \
+        fn<<<dim3(GRIDX_, heads, ptiles), warps * 32, smem, stream>>>((const T*)xbc, ldx, (const T*)dt_in, ld_dt, (const TP*)dt_bias, \
+                                                                      (const TP*)a_log, (const TP*)d_skip, state, slot_stride, slots, \
+                                                                      bounds, y, heads, vdim, N, groups, L, n_segments, scratch, decay); \
+    }
+    float* decay = scratch ? scratch + (size_t)stretches * heads * vdim * N : nullptr;
+    if (!scratch) {
+        ZI_SCAN_GO(0, n_segments)
+        return zi_check_launch("ssm_scan");
+    }
+    ZI_SCAN_GO(1, stretches)
+    const size_t all = (size_t)heads * vdim * N;
+    const int cb = (int)((all + 255) / 256 > 1024 ? 1024 : (all + 255) / 256);
+    ssm_combine_kernel<<<dim3(cb, n_segments), 256, 0, stream>>>(scratch, decay, state, slot_stride, slots, bounds, n_segments, heads,
+                                                                 vdim * N);
+    ZI_SCAN_GO(2, stretches)
+#undef ZI_SCAN_GO
+    return zi_check_launch("ssm_scan");
+}
+
+// How many stretches a step of n_tokens tokens in n_segments segments has at most, and the floats of scratch that the
+// stretch-wise form needs for them (states, then decay products).
+ZI_EXPORT int zi_ssm_scan_stretches(int n_tokens, int n_segments) { return n_tokens / SCAN_STRETCH + n_segments; }
+ZI_EXPORT long long zi_ssm_scan_scratch_floats(int n_tokens, int n_segments, int heads, int vdim, int N) {
+    return (long long)zi_ssm_scan_stretches(n_tokens, n_segments) * heads * ((long long)vdim * N + 1);
+}
+
+// scratch: null for the plain walk; else a buffer of zi_ssm_scan_scratch_floats(...) floats, and every segment's stretches
+// run side by side (bounds required).
 ZI_EXPORT int zi_ssm_scan(const void* xbc, int dtype, long long ldx, const void* dt_in, long long ld_dt, const void* dt_bias,
                           const void* a_log, const void* d_skip, int p_dtype, float* state, long long slot_stride,
-                          const int* slots, const int* bounds, float* y, int n_segments, int heads, int vdim, int N,
-                          int groups, cudaStream_t stream) {
+                          const int* slots, const int* bounds, float* y, int n_tokens, int n_segments, int heads, int vdim, int N,
+                          int groups, float* scratch, cudaStream_t stream) {
     if (n_segments <= 0) return 0;
     if (heads <= 0 || vdim <= 0 || N <= 0 || groups <= 0 || heads % groups)
         return zi_fail("ssm_scan: heads=%d vdim=%d state=%d groups=%d", heads, vdim, N, groups);
+    if (N > 512) return zi_fail("ssm_scan: state=%d is more than 512", N);
+    if (scratch && !bounds) return zi_fail("ssm_scan: the stretch-wise form needs the segments' bounds");
+    const int stretches = zi_ssm_scan_stretches(n_tokens, n_segments);
+    // the state's entries: blocks of 8 on as few lanes as take them (blocks of 16 beyond 256 entries, of 4 up to 4)
+    const int r4 = N > 256 ? 16 : (N <= 4 ? 4 : 8);
     int L = 1;
-    while ((N + L - 1) / L > SCAN_R && L < 32) L *= 2;
-    const int R = (N + L - 1) / L;
-    if (R > SCAN_R) return zi_fail("ssm_scan: state=%d is more than %d", N, 32 * SCAN_R);
-    const int pt = 32 / L;
-    int warps = (vdim + pt - 1) / pt;
-    if (warps > 8) warps = 8;
-    const int pc = warps * pt;
-    const int ptiles = (vdim + pc - 1) / pc;
-    int chunk = SCAN_CHUNK;
-    while (chunk > 1 && ((size_t)chunk * (2 * N + pc + 2)) * sizeof(float) > 40 * 1024) chunk /= 2;
-    const size_t smem = ((size_t)chunk * (2 * N + pc + 2)) * sizeof(float);
-    if (smem > 48 * 1024) return zi_fail("ssm_scan: state=%d needs %zu bytes of shared memory", N, smem);
-    if (heads > 65535 || ptiles > 65535) return zi_fail("ssm_scan: too many heads or columns for one launch");
-    dim3 grid(n_segments, heads, ptiles);
-    ZI_DISPATCH(dtype, T, ZI_DISPATCH(p_dtype, TP, {
-        ssm_scan_kernel<T, TP><<<grid, warps * 32, smem, stream>>>((const T*)xbc, ldx, (const T*)dt_in, ld_dt, (const TP*)dt_bias,
-                                                                   (const TP*)a_log, (const TP*)d_skip, state, slot_stride, slots,
-                                                                   bounds, y, heads, vdim, N, groups, L, R, chunk);
-    }););
-    return zi_check_launch("ssm_scan");
+    while (L * r4 < N) L *= 2;
+    const int cpt = vdim >= 4 ? 4 : 1;
+#define ZI_SCAN(R4_, CPT_) \
+    ZI_DISPATCH(dtype, T, ZI_DISPATCH(p_dtype, TP, { \
+        return ssm_scan_launch<T, TP, R4_, CPT_>(xbc, ldx, dt_in, ld_dt, dt_bias, a_log, d_skip, state, slot_stride, slots, bounds, y, \
+                                                 n_segments, heads, vdim, N, groups, L, stretches, scratch, stream); }););
+    if (cpt == 4) {
+        if (r4 == 4) { ZI_SCAN(4, 4) } else if (r4 == 8) { ZI_SCAN(8, 4) } else { ZI_SCAN(16, 4) }
+    } else {
+        if (r4 == 4) { ZI_SCAN(4, 1) } else if (r4 == 8) { ZI_SCAN(8, 1) } else { ZI_SCAN(16, 1) }
+    }
+#undef ZI_SCAN
+    return zi_fail("ssm_scan: no kernel for these sizes");
 }
 
 // ---------------------------------------------------------------------------------------

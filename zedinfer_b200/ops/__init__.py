@@ -1202,13 +1202,19 @@ def conv_state_update(u: torch.Tensor, taps: int, state: torch.Tensor, state_off
 
 def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
              state: torch.Tensor, slots: torch.Tensor, bounds: Optional[torch.Tensor], y: torch.Tensor, n_segments: int,
-             heads: int, vdim: int, n_state: int, groups: int) -> None:
+             heads: int, vdim: int, n_state: int, groups: int, stretchwise: bool = False) -> None:
     """The recurrence of a selective state-space layer over each segment's tokens in order, float32 throughout:
     ``dt = softplus(dt + dt_bias)``, ``S = exp(-exp(a_log) dt) S + dt B x^T``, ``y = S^T C + d_skip x``.  ``xbc [tokens, heads
     * vdim + 2 * groups * n_state]`` holds x, B and C; ``dt [tokens, heads]`` (rows of both may be strided); ``y`` float32
     ``[tokens, heads * vdim]``.  A request's state (``[heads, vdim, n_state]``, the first entries of its slot of ``state``) is
-    read at the start and written back at the end; slot -1: zero, not written."""
+    read at the start and written back at the end; slot -1: zero, not written.
+
+    ``stretchwise`` (needs ``bounds``): every segment is cut into stretches of 128 tokens that run side by side, first each
+    from a zero state, then, once a small kernel has carried the states through them in order, again with the outputs: the
+    same sums in another order, for long portions of prompts that would otherwise occupy a block per head and column tile."""
     need_cuda(xbc, dt, dt_bias, a_log, d_skip, state, slots, bounds, y)
+    if stretchwise and bounds is None:
+        raise KernelError("ssm_scan: the stretch-wise form needs the segments' bounds")
     need_int32("slots", slots)
     need_contiguous("y", y)
     n = xbc.shape[0]
@@ -1220,9 +1226,15 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: 
     if state.shape[1] < inner * n_state:
         raise KernelError("ssm_scan: the state slots are too small")
     sp, ss = _state_args(state, 0)
+    scratch = None
+    if stretchwise:
+        lib = _ssm.lib
+        lib.zi_ssm_scan_scratch_floats.restype = c_ll
+        floats = int(lib.zi_ssm_scan_scratch_floats(c_int(n), c_int(n_segments), c_int(heads), c_int(vdim), c_int(n_state)))
+        scratch = _grown_scratch(("ssm_scan", xbc.device), floats, xbc.device)
     _ssm.call("zi_ssm_scan", ptr(xbc), c_int(dtype_code(xbc.dtype)), c_ll(xbc.stride(0)), ptr(dt), c_ll(dt.stride(0)), ptr(dt_bias),
-              ptr(a_log), ptr(d_skip), c_int(dtype_code(dt_bias.dtype)), sp, ss, ptr(slots), ptr(bounds), ptr(y), c_int(n_segments),
-              c_int(heads), c_int(vdim), c_int(n_state), c_int(groups), stream())
+              ptr(a_log), ptr(d_skip), c_int(dtype_code(dt_bias.dtype)), sp, ss, ptr(slots), ptr(bounds), ptr(y), c_int(n),
+              c_int(n_segments), c_int(heads), c_int(vdim), c_int(n_state), c_int(groups), ptr(scratch), stream())
 
 
 def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, n_groups: int, eps: float, out: torch.Tensor) -> None:

@@ -25,6 +25,8 @@ from ..cache.manager import CallCacheView, StateNeed
 from ..weights.loader import TensorSpec
 from .base import Mixer, StepContext, register_mixer
 
+STRETCHWISE_MIN_TOKENS = 256      # steps of at least this many tokens (bfloat16) run their segments in stretches side by side
+
 _NAMES = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias", "a_log": "A_log", "d": "D", "norm": "norm",
           "o": "o"}
 
@@ -111,8 +113,10 @@ class Mamba2Mixer(Mixer):
         ops.causal_conv_silu(raw, self.w_conv, self.b_conv, state, self.state_elems, ctx.slots, tok_seg, ctx.positions, xbc)
         ops.conv_state_update(raw, self.taps, state, self.state_elems, ctx.slots, bounds, ctx.positions, ctx.n_segments)
         y = ctx.empty(n, inner, dtype=torch.float32)
+        # float32 steps walk every segment in one order whatever the cut; long bfloat16 portions run in stretches side by side
+        stretchwise = bounds is not None and x.dtype == torch.bfloat16 and n >= STRETCHWISE_MIN_TOKENS
         ops.ssm_scan(xbc, proj[:, inner + self.channels:], self.dt_bias, self.a_log, self.d, state, ctx.slots, bounds, y,
-                     ctx.n_segments, self.heads, self.vdim, self.n_state, self.groups)
+                     ctx.n_segments, self.heads, self.vdim, self.n_state, self.groups, stretchwise=stretchwise)
         out = ctx.empty(n, inner)
         ops.gated_group_rmsnorm(y, proj[:, :inner], self.g, self.norm_groups, self.eps, out)
         return out
