@@ -89,7 +89,18 @@ def all_chosen(cfg):
     return out
 
 
-CONFIGS = {"A": (GB_A, 31), "B": (GB_B, 32), "C": (GB_C, 33), "D": (GB_D, 34)}
+# state-space layers alone (no paged cache at all), run twice; and a model of attention alone with a head size of 24
+GB_E = {
+    "architecture": "Gibalorn", "vocab": 120, "width": 48, "norm": {"eps": 1e-5},
+    "layers": [_with(_mamba(2, 16, 24, 2, 3, 2), _moe(3, 2, 32)), _with(_mamba(5, 4, 12, 1, 2, 1), None)],
+    "loop": {"start": 0, "stop": 2, "times": 2},
+}
+GB_F = {
+    "architecture": "Gibalorn", "vocab": 99, "width": 40, "norm": {"eps": 1e-6},
+    "layers": [_with(_attn(2, 1, 24, 12, 64.0, 0.2), _moe(2, 1, 16)), _with(_latent(2, 8, 4, 8, 536, 8, 99.0, 0.3), None)],
+    "loop": None,
+}
+CONFIGS = {"A": (GB_A, 31), "B": (GB_B, 32), "C": (GB_C, 33), "D": (GB_D, 34), "E": (GB_E, 35), "F": (GB_F, 36)}
 CONFIGS.update({name + "x": (all_chosen(cfg), seed) for name, (cfg, seed) in list(CONFIGS.items())})
 INIT_SCALE = 5.0
 

@@ -527,8 +527,8 @@ def judge(got, exp, dtype):
     assert all(e <= 4 * tol for e in errs.values()), max(errs.values())
 
 
-LENGTHS = {"A": [7, 13, 95, 45], "B": [1, 17, 120, 64], "C": [110, 5, 60], "D": [50, 2, 61]}
-PAGES = {"A": 4, "B": 16, "C": 16, "D": 8}
+LENGTHS = {"A": [7, 13, 95, 45], "B": [1, 17, 120, 64], "C": [110, 5, 60], "D": [50, 2, 61], "E": [40, 3, 70], "F": [33, 1, 52]}
+PAGES = {"A": 4, "B": 16, "C": 16, "D": 8, "E": 8, "F": 8}
 
 
 def test_the_run_order_and_the_caches_of_every_pass(models):
@@ -548,7 +548,7 @@ def test_the_run_order_and_the_caches_of_every_pass(models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("family", ["whole", "tail", "chunks", "mixed"])
 def test_cuts_match_plain(models, name, dtype, family):
     """Whole prompts; a tail decoded token by token; portions down to two tokens; mixed batches of unequal requests in a
@@ -563,12 +563,12 @@ def test_cuts_match_plain(models, name, dtype, family):
         steps = {"whole": traces.whole, "chunks": traces.chunks, "mixed": traces.mixed}[family](requests)
     page = PAGES[name]
     need = traces.max_live_tokens(steps, round_to=page)
-    core = EngineCore(model, dtype, page_size=page, num_pages=need // page, max_requests=4)
+    core = EngineCore(model, dtype, page_size=page, num_pages=max(1, need // page), max_requests=4)
     got = run_trace(core, steps)
     core.check_kernels()
     judge(got, expected_logits(model, requests), dtype)
     assert core.cache.num_live == 0 and all(g.pool.num_used == 0 for g in core.cache.groups)
-    assert core.cache.slots.num_free_slots == 4
+    assert core.cache.slots.num_free_slots == core.cache.slots.num_slots           # 4 where the model keeps state, else none
 
 
 @pytest.mark.parametrize("graphs", [False, True])

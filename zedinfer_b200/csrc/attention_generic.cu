@@ -1,5 +1,5 @@
 // Paged causal attention, one warp per (query token, query head); float32 or bfloat16 storage,
-// float32 arithmetic.  Takes any head_dim that is a multiple of 8 up to 512, any number of
+// float32 arithmetic.  Takes any head_dim that is a multiple of 8 up to 1024, any number of
 // heads and groups, any page size, and an optional window.
 //
 // This kernel is the whole 32-bit path and the general fallback of the bfloat16 path.  A query
@@ -19,7 +19,7 @@
 ZI_DEFINE_LAST_ERROR(attention_generic)
 
 #define WARPS 4
-// A lane keeps head_dim / 32 output elements: 8 registers up to head_dim 256, 16 up to 512.
+// A lane keeps head_dim / 32 output elements: 8 registers up to head_dim 256, 16 up to 512, 32 up to 1024.
 
 template <typename T, int MAX_DREG>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -103,8 +103,8 @@ ZI_EXPORT int zi_paged_attention(const void* q, const void* cache, void* out, in
                                  long long kv_stride, int window, float scale, const float* sinks,
                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (head_dim <= 0 || head_dim % 8 != 0 || head_dim > 512)
-        return zi_fail("attention: head_dim=%d must be a multiple of 8 and at most %d", head_dim, 512);
+    if (head_dim <= 0 || head_dim % 8 != 0 || head_dim > 1024)
+        return zi_fail("attention: head_dim=%d must be a multiple of 8 and at most %d", head_dim, 1024);
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         return zi_fail("attention: %d query heads cannot share %d key/value heads", n_heads, n_kv_heads);
     if (page_size <= 0 || max_blocks <= 0) return zi_fail("attention: page_size=%d max_blocks=%d", page_size, max_blocks);
@@ -117,8 +117,12 @@ ZI_EXPORT int zi_paged_attention(const void* q, const void* cache, void* out, in
             paged_attention_kernel<T, 8><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(
                 (const T*)q, (const T*)cache, (T*)out, tables, tok_seg, pos, n_tokens, n_heads, n_kv_heads, head_dim,
                 page_size, max_blocks, page_stride, kv_stride, window, scale, sinks);
-        else
+        else if (head_dim <= 512)
             paged_attention_kernel<T, 16><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(
+                (const T*)q, (const T*)cache, (T*)out, tables, tok_seg, pos, n_tokens, n_heads, n_kv_heads, head_dim,
+                page_size, max_blocks, page_stride, kv_stride, window, scale, sinks);
+        else
+            paged_attention_kernel<T, 32><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(
                 (const T*)q, (const T*)cache, (T*)out, tables, tok_seg, pos, n_tokens, n_heads, n_kv_heads, head_dim,
                 page_size, max_blocks, page_stride, kv_stride, window, scale, sinks);
     });

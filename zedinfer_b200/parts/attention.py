@@ -43,9 +43,11 @@ class AttentionMixer(Mixer):
                  unit_sink: bool = False, names: Optional[Mapping[str, str]] = None):
         if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} query heads cannot share {num_kv_heads} key/value heads")
-        if head_dim <= 0 or head_dim % 16:
+        # a rule that turns a span of the head (its own kernel) takes steps of 8; the rotate-half kernels steps of 16
+        step = 8 if position.kind == "rope_span" else 16
+        if head_dim <= 0 or head_dim % step:
             raise ValueError(f"attention: head_dim={head_dim} is not supported; the kernels take head sizes "
-                             f"in steps of 16 (16, 32, ..., 256)")
+                             f"in steps of {step} ({step}, {2 * step}, ..., 256)")
         if head_dim > 256:
             raise ValueError(f"attention: head_dim={head_dim} is not supported; the kernels take at most 256")
         if window is not None and window <= 0:

@@ -62,9 +62,9 @@ class LatentAttentionMixer(Mixer):
             raise ValueError(f"latent_attention: {rot_dims} of {rot_dim} rotated key entries cannot turn (an even number, at most all)")
         if rot_dim == 0 and (rank <= 0 or rank % 8 or rank > 512):
             raise ValueError(f"latent_attention: rank={rank} is not supported; the kernels take multiples of 8 up to 512")
-        if rank <= 0 or rank + rot_dim > 512:
+        if rank <= 0 or rank + rot_dim > 1024:
             raise ValueError(f"latent_attention: rank={rank} with {rot_dim} rotated entries is not supported; the kernels take "
-                             f"cache rows of at most 512 entries")
+                             f"cache rows of at most 1024 entries")
         if q_rank is not None and q_rank <= 0:
             raise ValueError(f"latent_attention: q_rank={q_rank} must be positive (or None for a direct query projection)")
         if window is not None and window <= 0:
