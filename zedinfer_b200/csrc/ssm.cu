@@ -64,14 +64,62 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ u, long long ldu, 
     }
 }
 
+// The same, eight neighbouring channels per thread with 16- or 32-byte accesses (channels % 8 == 0, aligned rows); the same
+// sums in the same order.
+template <typename T, typename TW>
+__global__ void causal_conv_silu_vec8_kernel(const T* __restrict__ u, long long ldu, const TW* __restrict__ w,
+                                             const TW* __restrict__ bias, const float* __restrict__ state, long long slot_stride,
+                                             const int* __restrict__ slots, const int* __restrict__ tok_seg,
+                                             const int* __restrict__ pos, T* __restrict__ out, int n_tokens, int channels, int taps) {
+    const int n = blockIdx.y;
+    const int seg = tok_seg ? tok_seg[n] : n;
+    const int p = pos[n];
+    const int slot = slots[seg];
+    for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8; c < channels; c += gridDim.x * blockDim.x * 8) {
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = bias ? to_f32<TW>(bias[c + e]) : 0.0f;
+        for (int j = 0; j < taps; ++j) {
+            const int back = taps - 1 - j;
+            const int q = p - back;
+            if (q < 0) continue;
+            float v[8];
+            const bool here = back == 0 || (n - back >= 0 && (tok_seg ? tok_seg[n - back] == seg : false));
+            if (here) {
+                load8(u + (size_t)(n - back) * ldu + c, v);
+            } else if (slot >= 0) {
+                const float* sp = state + (size_t)slot * slot_stride + (size_t)(q % (taps - 1)) * channels + c;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = sp[e];
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(to_f32<TW>(w[(size_t)(c + e) * taps + j]), v[e], acc[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
+        store8(out + (size_t)n * channels + c, acc);
+    }
+}
+
 ZI_EXPORT int zi_causal_conv_silu(const void* u, int dtype, long long ldu, const void* w, const void* bias, int w_dtype,
                                   const float* state, long long slot_stride, const int* slots, const int* tok_seg,
                                   const int* pos, void* out, int n_tokens, int channels, int taps, cudaStream_t stream) {
     if (n_tokens <= 0 || channels <= 0) return 0;
     if (taps <= 0) return zi_fail("causal_conv: taps=%d must be positive", taps);
-    if (n_tokens > 65535 * 32) return zi_fail("causal_conv: too many tokens for one launch");
+    if (n_tokens > 65535) return zi_fail("causal_conv: %d tokens are too many for one launch", n_tokens);
+    const size_t align = dtype == ZI_BF16 ? 16 : 32;
+    if (channels % 8 == 0 && ldu % 8 == 0 && ((uintptr_t)u % align) == 0 && ((uintptr_t)out % align) == 0) {
+        dim3 grid((channels / 8 + 127) / 128, n_tokens);
+        ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {
+            causal_conv_silu_vec8_kernel<T, TW><<<grid, 128, 0, stream>>>((const T*)u, ldu, (const TW*)w, (const TW*)bias, state,
+                                                                          slot_stride, slots, tok_seg, pos, (T*)out, n_tokens, channels, taps);
+        }););
+        return zi_check_launch("causal_conv_silu");
+    }
     dim3 grid((channels + 255) / 256, n_tokens);
-    if (grid.y > 65535) return zi_fail("causal_conv: %d tokens are too many for one launch", n_tokens);
     ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {
         causal_conv_silu_kernel<T, TW><<<grid, 256, 0, stream>>>((const T*)u, ldu, (const TW*)w, (const TW*)bias, state, slot_stride,
                                                                  slots, tok_seg, pos, (T*)out, n_tokens, channels, taps);
@@ -131,6 +179,13 @@ ZI_EXPORT int zi_conv_state_update(const void* u, int dtype, long long ldu, floa
 
 __device__ __forceinline__ float softplus_f32(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
 
+// Two float32 in one 64-bit register and the packed arithmetic of sm_100 on them: one instruction for two values, each
+// rounded as the scalar instruction rounds it.
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) { uint64_t r; asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) { uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b)); return d; }
+
 // Which (segment, tokens) a block of a stretch-wise launch works on: stretch number `id` counted through the segments.
 __device__ __forceinline__ bool find_stretch(const int* __restrict__ bounds, int n_segments, int id, int* seg, int* first, int* end) {
     for (int s = 0; s < n_segments; ++s) {
@@ -148,7 +203,7 @@ __device__ __forceinline__ bool find_stretch(const int* __restrict__ bounds, int
 }
 
 template <typename T, typename TP, int R4, int CPT, int MODE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, R4 <= 8 ? 3 : 1)
 ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ dt_in, long long ld_dt,
                 const TP* __restrict__ dt_bias, const TP* __restrict__ a_log, const TP* __restrict__ d_skip,
                 float* __restrict__ state, long long slot_stride, const int* __restrict__ slots,
@@ -178,7 +233,7 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
     float* decs = dts + SCAN_CHUNK;                  // [chunk]
     for (int i = threadIdx.x; i < 2 * SCAN_CHUNK * row; i += blockDim.x) sm[i] = 0.0f;     // entries beyond N stay zero
     const float a_rate = expf(to_f32<TP>(a_log[h])), bias = to_f32<TP>(dt_bias[h]), skip = to_f32<TP>(d_skip[h]);
-    float S[CPT][R4];
+    uint64_t S[CPT][R4 / 2];                         // pairs of neighbouring entries
     // where this block's state comes from and goes to: the request's slot, or the stretch's place in the scratch buffer
     float* sbase;
     bool vec;
@@ -207,7 +262,8 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
                     if (nl * R4 + r + 3 < N) v.w = src[r + 3];
                 }
             }
-            S[c][r] = v.x; S[c][r + 1] = v.y; S[c][r + 2] = v.z; S[c][r + 3] = v.w;
+            S[c][r / 2] = f2_pack(v.x, v.y);
+            S[c][r / 2 + 1] = f2_pack(v.z, v.w);
         }
     }
     // eight values per load where everything is a multiple of eight and aligned for it
@@ -220,11 +276,11 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
         if (vec8) {
             // per token: N / 8 pieces of B, as many of C (MODE 1 needs none), pc / 8 of x; all of a round's loads before its stores
             const int nb = N >> 3, per = (MODE == 1 ? nb : 2 * nb) + (pc >> 3), items = cnt * per;
-            for (int i0 = threadIdx.x; i0 < items; i0 += 4 * blockDim.x) {
-                float v[4][8];
-                int at[4];
+            for (int i0 = threadIdx.x; i0 < items; i0 += 2 * blockDim.x) {
+                float v[2][8];
+                int at[2];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
+                for (int q = 0; q < 2; ++q) {
                     const int i = i0 + q * blockDim.x;
                     at[q] = -1;
                     if (i < items) {
@@ -247,7 +303,7 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
                     }
                 }
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
+                for (int q = 0; q < 2; ++q)
                     if (at[q] >= 0) {
                         // eight values lie in one block of R4 = 8 or 16, or in two blocks of 4
                         *reinterpret_cast<float4*>(sm + at[q]) = make_float4(v[q][0], v[q][1], v[q][2], v[q][3]);
@@ -276,31 +332,45 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
         for (int t = 0; t < cnt; ++t) {
             const float a = decs[t], dt = dts[t];
             if (MODE == 1) decay_all *= a;
-            float xv[CPT], dx[CPT], acc[CPT];
+            float xv[CPT], acc[CPT];
+            uint64_t dx2[CPT], acc2[CPT];
+            const uint64_t a2 = f2_pack(a, a);
 #pragma unroll
-            for (int c = 0; c < CPT; ++c) { xv[c] = xs[t * pc + col + c]; dx[c] = dt * xv[c]; acc[c] = 0.0f; }
+            for (int c = 0; c < CPT; ++c) {
+                xv[c] = xs[t * pc + col + c];
+                const float dx = dt * xv[c];
+                dx2[c] = f2_pack(dx, dx);
+                acc2[c] = 0ull;
+            }
             const float* bt = Bs + t * row + nl * RS;
             const float* ct = Cs + t * row + nl * RS;
+            // entries 2i and 2i + 1 of a block go through the packed instructions side by side; a column's sum over the block
+            // is (the even entries in order) + (the odd entries in order)
 #pragma unroll
             for (int r = 0; r < R4; r += 4) {
-                const float4 b4 = *reinterpret_cast<const float4*>(bt + r);
-                const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+                const ulonglong2 b4 = *reinterpret_cast<const ulonglong2*>(bt + r);
                 if (MODE == 1) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e)
-#pragma unroll
-                        for (int c = 0; c < CPT; ++c) S[c][r + e] = fmaf(dx[c], bv[e], a * S[c][r + e]);
+                    for (int c = 0; c < CPT; ++c) {
+                        S[c][r / 2] = f2_fma(dx2[c], b4.x, f2_mul(a2, S[c][r / 2]));
+                        S[c][r / 2 + 1] = f2_fma(dx2[c], b4.y, f2_mul(a2, S[c][r / 2 + 1]));
+                    }
                     continue;
                 }
-                const float4 c4 = *reinterpret_cast<const float4*>(ct + r);
-                const float cv[4] = {c4.x, c4.y, c4.z, c4.w};
+                const ulonglong2 c4 = *reinterpret_cast<const ulonglong2*>(ct + r);
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
+                for (int c = 0; c < CPT; ++c) {
+                    S[c][r / 2] = f2_fma(dx2[c], b4.x, f2_mul(a2, S[c][r / 2]));
+                    acc2[c] = f2_fma(S[c][r / 2], c4.x, acc2[c]);
+                    S[c][r / 2 + 1] = f2_fma(dx2[c], b4.y, f2_mul(a2, S[c][r / 2 + 1]));
+                    acc2[c] = f2_fma(S[c][r / 2 + 1], c4.y, acc2[c]);
+                }
+            }
 #pragma unroll
-                    for (int c = 0; c < CPT; ++c) {
-                        S[c][r + e] = fmaf(dx[c], bv[e], a * S[c][r + e]);
-                        acc[c] = fmaf(S[c][r + e], cv[e], acc[c]);
-                    }
+            for (int c = 0; c < CPT; ++c) {
+                float lo, hi;
+                f2_unpack(acc2[c], lo, hi);
+                acc[c] = lo + hi;
             }
             if (MODE == 1) continue;
             if (CPT == 4 && L >= 4) {
@@ -335,12 +405,15 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
         float* dst = sbase + (size_t)(p0 + c) * N + nl * R4;
 #pragma unroll
         for (int r = 0; r < R4; r += 4) {
+            float e4[4];
+            f2_unpack(S[c][r / 2], e4[0], e4[1]);
+            f2_unpack(S[c][r / 2 + 1], e4[2], e4[3]);
             if (vec) {
-                if (nl * R4 + r < N) *reinterpret_cast<float4*>(dst + r) = make_float4(S[c][r], S[c][r + 1], S[c][r + 2], S[c][r + 3]);
+                if (nl * R4 + r < N) *reinterpret_cast<float4*>(dst + r) = make_float4(e4[0], e4[1], e4[2], e4[3]);
             } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    if (nl * R4 + r + e < N) dst[r + e] = S[c][r + e];
+                    if (nl * R4 + r + e < N) dst[r + e] = e4[e];
             }
         }
     }
