@@ -38,12 +38,15 @@ ZI_EXPORT int zi_segment_bounds(const int* tok_seg, int n_tokens, int n_segments
 // ---------------------------------------------------------------------------------------
 // out[n, c] = silu(bias[c] + sum_j w[c, j] * u(pos[n] - (taps - 1) + j)), j rising; u from this step's rows where the
 // position lies in the segment's portion, else from the slot's ring, zero before position 0.
+// update_state (a step of single tokens only, tok_seg null): the kernel also puts every token's input into its ring, which
+// zi_conv_state_update does otherwise.
 // ---------------------------------------------------------------------------------------
 template <typename T, typename TW>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ u, long long ldu, const TW* __restrict__ w,
-                                        const TW* __restrict__ bias, const float* __restrict__ state, long long slot_stride,
+                                        const TW* __restrict__ bias, const float* state, long long slot_stride,
                                         const int* __restrict__ slots, const int* __restrict__ tok_seg,
-                                        const int* __restrict__ pos, T* __restrict__ out, int n_tokens, int channels, int taps) {
+                                        const int* __restrict__ pos, T* __restrict__ out, int n_tokens, int channels, int taps,
+                                        float* ring   /* the same memory as `state` when given: no restrict on either */) {
     const int n = blockIdx.y;
     const int seg = tok_seg ? tok_seg[n] : n;
     const int p = pos[n];
@@ -61,25 +64,42 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ u, long long ldu, 
             acc = fmaf(to_f32<TW>(w[(size_t)c * taps + j]), v, acc);
         }
         out[(size_t)n * channels + c] = from_f32<T>(acc / (1.0f + expf(-acc)));
+        // a step of single tokens: this thread alone read its channel's ring, so it may put the token's input there itself
+        if (ring && slot >= 0 && taps > 1)
+            ring[(size_t)slot * slot_stride + (size_t)(p % (taps - 1)) * channels + c] = to_f32<T>(u[(size_t)n * ldu + c]);
     }
 }
 
 // The same, eight neighbouring channels per thread with 16- or 32-byte accesses (channels % 8 == 0, aligned rows); the same
 // sums in the same order.
-template <typename T, typename TW>
+template <typename T, typename TW, int TAPS>
 __global__ void causal_conv_silu_vec8_kernel(const T* __restrict__ u, long long ldu, const TW* __restrict__ w,
-                                             const TW* __restrict__ bias, const float* __restrict__ state, long long slot_stride,
+                                             const TW* __restrict__ bias, const float* state, long long slot_stride,
                                              const int* __restrict__ slots, const int* __restrict__ tok_seg,
-                                             const int* __restrict__ pos, T* __restrict__ out, int n_tokens, int channels, int taps) {
+                                             const int* __restrict__ pos, T* __restrict__ out, int n_tokens, int channels, int taps,
+                                             float* ring   /* the same memory as `state` when given: no restrict on either */) {
     const int n = blockIdx.y;
     const int seg = tok_seg ? tok_seg[n] : n;
     const int p = pos[n];
     const int slot = slots[seg];
+    if (TAPS > 0) taps = TAPS;
     for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8; c < channels; c += gridDim.x * blockDim.x * 8) {
         float acc[8];
+        // the eight channels' weights are 8 * taps consecutive values: whole vectors where the number of taps is known
+        float wv[TAPS > 0 ? TAPS : 1][8];
+        if (TAPS > 0) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = bias ? to_f32<TW>(bias[c + e]) : 0.0f;
-        for (int j = 0; j < taps; ++j) {
+            for (int k = 0; k < TAPS; ++k) load8(w + (size_t)c * TAPS + k * 8, wv[k]);
+            if (bias) load8(bias + c, acc);
+            else
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = bias ? to_f32<TW>(bias[c + e]) : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < (TAPS > 0 ? TAPS : taps); ++j) {
             const int back = taps - 1 - j;
             const int q = p - back;
             if (q < 0) continue;
@@ -96,33 +116,53 @@ __global__ void causal_conv_silu_vec8_kernel(const T* __restrict__ u, long long 
                 for (int e = 0; e < 8; ++e) v[e] = 0.0f;
             }
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = fmaf(to_f32<TW>(w[(size_t)(c + e) * taps + j]), v[e], acc[e]);
+            for (int e = 0; e < 8; ++e) {
+                const float wt = TAPS > 0 ? wv[(e * (TAPS > 0 ? TAPS : 1) + j) / 8][(e * (TAPS > 0 ? TAPS : 1) + j) % 8]
+                                          : to_f32<TW>(w[(size_t)(c + e) * taps + j]);
+                acc[e] = fmaf(wt, v[e], acc[e]);
+            }
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
         store8(out + (size_t)n * channels + c, acc);
+        if (ring && slot >= 0 && taps > 1) {
+            float v[8];
+            load8(u + (size_t)n * ldu + c, v);
+            float* dst = ring + (size_t)slot * slot_stride + (size_t)(p % (taps - 1)) * channels + c;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dst[e] = v[e];
+        }
     }
 }
 
 ZI_EXPORT int zi_causal_conv_silu(const void* u, int dtype, long long ldu, const void* w, const void* bias, int w_dtype,
-                                  const float* state, long long slot_stride, const int* slots, const int* tok_seg,
-                                  const int* pos, void* out, int n_tokens, int channels, int taps, cudaStream_t stream) {
+                                  float* state, long long slot_stride, const int* slots, const int* tok_seg,
+                                  const int* pos, void* out, int n_tokens, int channels, int taps, int update_state,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0 || channels <= 0) return 0;
     if (taps <= 0) return zi_fail("causal_conv: taps=%d must be positive", taps);
+    if (update_state && tok_seg) return zi_fail("causal_conv: only a step of single tokens may update the state on the way");
+    float* ring = update_state ? state : nullptr;
     if (n_tokens > 65535) return zi_fail("causal_conv: %d tokens are too many for one launch", n_tokens);
     const size_t align = dtype == ZI_BF16 ? 16 : 32;
     if (channels % 8 == 0 && ldu % 8 == 0 && ((uintptr_t)u % align) == 0 && ((uintptr_t)out % align) == 0) {
         dim3 grid((channels / 8 + 127) / 128, n_tokens);
-        ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {
-            causal_conv_silu_vec8_kernel<T, TW><<<grid, 128, 0, stream>>>((const T*)u, ldu, (const TW*)w, (const TW*)bias, state,
-                                                                          slot_stride, slots, tok_seg, pos, (T*)out, n_tokens, channels, taps);
+        const size_t walign = w_dtype == ZI_BF16 ? 16 : 32;
+        const bool wvec = ((uintptr_t)w % walign) == 0 && (!bias || ((uintptr_t)bias % walign) == 0);
+#define ZI_CONV(TAPS_)                                                                                                            \
+        ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {                                                                          \
+            causal_conv_silu_vec8_kernel<T, TW, TAPS_><<<grid, 128, 0, stream>>>((const T*)u, ldu, (const TW*)w, (const TW*)bias, state, \
+                                                                                 slot_stride, slots, tok_seg, pos, (T*)out, n_tokens, \
+                                                                                 channels, taps, ring);                          \
         }););
+        if (wvec && taps == 4) { ZI_CONV(4) } else if (wvec && taps == 3) { ZI_CONV(3) } else if (wvec && taps == 2) { ZI_CONV(2) } else { ZI_CONV(0) }
+#undef ZI_CONV
         return zi_check_launch("causal_conv_silu");
     }
     dim3 grid((channels + 255) / 256, n_tokens);
     ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {
         causal_conv_silu_kernel<T, TW><<<grid, 256, 0, stream>>>((const T*)u, ldu, (const TW*)w, (const TW*)bias, state, slot_stride,
-                                                                 slots, tok_seg, pos, (T*)out, n_tokens, channels, taps);
+                                                                 slots, tok_seg, pos, (T*)out, n_tokens, channels, taps, ring);
     }););
     return zi_check_launch("causal_conv_silu");
 }

@@ -1171,11 +1171,15 @@ def _state_args(state: torch.Tensor, offset: int):
 
 
 def causal_conv_silu(u: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, state_offset: int,
-                     slots: torch.Tensor, tok_seg: Optional[torch.Tensor], pos: torch.Tensor, out: torch.Tensor) -> None:
+                     slots: torch.Tensor, tok_seg: Optional[torch.Tensor], pos: torch.Tensor, out: torch.Tensor,
+                     update_state: bool = False) -> None:
     """``out[n, c] = silu(bias[c] + sum_j w[c, j] * u_c(pos[n] - (taps - 1) + j))``: a causal convolution per channel over
     each request's tokens.  Inputs of this step come from ``u`` (``[tokens, channels]``, rows may be strided), earlier ones
     from the request's slot of ``state`` (float32 ``[slots, entries]``; the ring ``[taps - 1, channels]`` starts at entry
-    ``state_offset``), and what lies before position 0 is zero.  ``tok_seg`` None: token n is segment n."""
+    ``state_offset``), and what lies before position 0 is zero.  ``tok_seg`` None: token n is segment n.  ``update_state``
+    (only with ``tok_seg`` None): every token's input also goes into its ring, as :func:`conv_state_update` does otherwise."""
+    if update_state and tok_seg is not None:
+        raise KernelError("causal_conv_silu: only a step of single tokens may update the state on the way")
     need_cuda(u, w, bias, state, slots, tok_seg, pos, out)
     need_int32("slots", slots), need_int32("pos", pos)
     need_contiguous("w", w), need_contiguous("out", out)
@@ -1184,7 +1188,8 @@ def causal_conv_silu(u: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
         raise KernelError(f"causal_conv_silu: u {tuple(u.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
     sp, ss = _state_args(state, state_offset)
     _ssm.call("zi_causal_conv_silu", ptr(u), c_int(dtype_code(u.dtype)), c_ll(u.stride(0)), ptr(w), ptr(bias), c_int(dtype_code(w.dtype)),
-              sp, ss, ptr(slots), ptr(tok_seg), ptr(pos), ptr(out), c_int(n), c_int(ch), c_int(w.shape[1]), stream())
+              sp, ss, ptr(slots), ptr(tok_seg), ptr(pos), ptr(out), c_int(n), c_int(ch), c_int(w.shape[1]),
+              c_int(1 if update_state else 0), stream())
 
 
 def conv_state_update(u: torch.Tensor, taps: int, state: torch.Tensor, state_offset: int, slots: torch.Tensor,

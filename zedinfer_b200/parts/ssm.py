@@ -110,8 +110,13 @@ class Mamba2Mixer(Mixer):
         bounds = step_segment_bounds(ctx)
         tok_seg = None if ctx.decode_only else ctx.tok_seg
         xbc = ctx.empty(n, self.channels)
-        ops.causal_conv_silu(raw, self.w_conv, self.b_conv, state, self.state_elems, ctx.slots, tok_seg, ctx.positions, xbc)
-        ops.conv_state_update(raw, self.taps, state, self.state_elems, ctx.slots, bounds, ctx.positions, ctx.n_segments)
+        # a step of single tokens: a thread reads its channel's ring alone, so it writes the token's input there itself;
+        # otherwise the ring is written by a second launch, once every token of the portion has read it
+        single = tok_seg is None
+        ops.causal_conv_silu(raw, self.w_conv, self.b_conv, state, self.state_elems, ctx.slots, tok_seg, ctx.positions, xbc,
+                             update_state=single)
+        if not single:
+            ops.conv_state_update(raw, self.taps, state, self.state_elems, ctx.slots, bounds, ctx.positions, ctx.n_segments)
         y = ctx.empty(n, inner, dtype=torch.float32)
         # float32 steps walk every segment in one order whatever the cut; long bfloat16 portions run in stretches side by side
         stretchwise = bounds is not None and x.dtype == torch.bfloat16 and n >= STRETCHWISE_MIN_TOKENS
