@@ -277,6 +277,88 @@ rotary_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ q_out, lon
     }
 }
 
+// The same with 8 entries per access, where head size, span and its offset are multiples of 8 (16 for the span in the
+// rotate-half pairing) and every row is aligned for it: a thread takes 8 neighbouring entries (interleaved pairing: four
+// pairs inside them), or 8 entries of the span's first half and the 8 that pair with them, or 8 entries outside the span.
+// The arithmetic per pair is rotate_pair as above: the same bits.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotary_vec8_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ q_out, long long ldq, T* __restrict__ cache,
+                   const int* __restrict__ tables, const int* __restrict__ tok_seg, const int* __restrict__ pos,
+                   const float* __restrict__ inv_freq, int n_q, int n_k, int head_dim, int rot_offset, int rot_dims,
+                   int interleaved, int v_mode, int page_size, int max_blocks, long long page_stride, long long kv_stride) {
+    extern __shared__ float cs[];            // cos[half], sin[half]
+    const int n = blockIdx.x;
+    const int half = rot_dims >> 1;
+    const int p = pos[n];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)p * inv_freq[i], &s, &c);
+        cs[i] = c;
+        cs[half + i] = s;
+    }
+    __syncthreads();
+    T* page_base = nullptr;
+    if (cache) {
+        const int seg = tok_seg ? tok_seg[n] : n;
+        const int page = tables[(size_t)seg * max_blocks + p / page_size];
+        page_base = cache + (size_t)page * page_stride + (size_t)(p % page_size) * head_dim;
+    }
+    const T* row = x + (size_t)n * ldx;
+    const int span_units = interleaved ? rot_dims >> 3 : half >> 3;
+    const int units = span_units + ((head_dim - rot_dims) >> 3);
+    const int heads = n_q + (cache ? n_k * (v_mode == 1 ? 2 : 1) : 0);
+    for (int idx = threadIdx.x; idx < heads * units; idx += blockDim.x) {
+        const int h = idx / units, u = idx - h * units;
+        const T* src = row + (size_t)h * head_dim;
+        T* dst;
+        T* raw = nullptr;
+        bool turn = true;
+        if (h < n_q) {
+            dst = q_out + (size_t)n * ldq + (size_t)h * head_dim;
+        } else if (h < n_q + n_k) {
+            dst = page_base + (size_t)(h - n_q) * page_size * head_dim;
+            if (v_mode == 2) raw = dst + kv_stride;
+        } else {
+            dst = page_base + kv_stride + (size_t)(h - n_q - n_k) * page_size * head_dim;
+            turn = false;
+        }
+        if (u >= span_units) {                                  // 8 entries outside the span
+            int d = (u - span_units) * 8;
+            if (d >= rot_offset) d += rot_dims;
+            float v[8];
+            load8(src + d, v);
+            if (raw) store8(raw + d, v);
+            if (dst != src) store8(dst + d, v);
+        } else if (interleaved) {                               // four pairs inside 8 neighbouring entries
+            const int d = rot_offset + u * 8, i0 = u * 4;
+            float v[8], o[8];
+            load8(src + d, v);
+            if (raw) store8(raw + d, v);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (turn) rotate_pair(v[2 * k], v[2 * k + 1], cs[i0 + k], cs[half + i0 + k], &o[2 * k], &o[2 * k + 1]);
+                else { o[2 * k] = v[2 * k]; o[2 * k + 1] = v[2 * k + 1]; }
+            }
+            // what the scalar kernel stores is the rounded value; store8 rounds the same way
+            store8(dst + d, o);
+        } else {                                                // 8 entries of the first half and their partners
+            const int lo_at = rot_offset + u * 8, hi_at = lo_at + half, i0 = u * 8;
+            float a[8], b[8], lo[8], hi[8];
+            load8(src + lo_at, a);
+            load8(src + hi_at, b);
+            if (raw) { store8(raw + lo_at, a); store8(raw + hi_at, b); }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (turn) rotate_pair(a[k], b[k], cs[i0 + k], cs[half + i0 + k], &lo[k], &hi[k]);
+                else { lo[k] = a[k]; hi[k] = b[k]; }
+            }
+            store8(dst + lo_at, lo);
+            store8(dst + hi_at, hi);
+        }
+    }
+}
+
 ZI_EXPORT int zi_rotary(const void* x, int dtype, long long ldx, void* q_out, long long ldq, void* cache, const int* tables,
                         const int* tok_seg, const int* pos, const float* inv_freq, int n_tokens, int n_q, int n_k, int head_dim,
                         int rot_offset, int rot_dims, int interleaved, int v_mode, int page_size, int max_blocks,
@@ -288,6 +370,18 @@ ZI_EXPORT int zi_rotary(const void* x, int dtype, long long ldx, void* q_out, lo
     if (cache && (page_size <= 0 || max_blocks <= 0 || !tables)) return zi_fail("rotary: the cache append needs tables and a page size");
     if (cache && v_mode == 2 && kv_stride == 0) return zi_fail("rotary: unrotated keys as values need a second plane");
     const size_t smem = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
+    const size_t align = dtype == ZI_BF16 ? 16 : 32;
+    const bool vec8 = head_dim % 8 == 0 && rot_offset % 8 == 0 && rot_dims % (interleaved ? 8 : 16) == 0 && ldx % 8 == 0 && ldq % 8 == 0 &&
+                      ((uintptr_t)x % align) == 0 && ((uintptr_t)q_out % align) == 0 &&
+                      (!cache || (((uintptr_t)cache % align) == 0 && page_stride % 8 == 0 && kv_stride % 8 == 0));
+    if (vec8) {
+        ZI_DISPATCH(dtype, T, {
+            rotary_vec8_kernel<T><<<n_tokens, 128, smem, stream>>>((const T*)x, ldx, (T*)q_out, ldq, (T*)cache, tables, tok_seg, pos,
+                                                                   inv_freq, n_q, n_k, head_dim, rot_offset, rot_dims, interleaved, v_mode,
+                                                                   page_size, max_blocks, page_stride, kv_stride);
+        });
+        return zi_check_launch("rotary");
+    }
     ZI_DISPATCH(dtype, T, {
         rotary_kernel<T><<<n_tokens, 256, smem, stream>>>((const T*)x, ldx, (T*)q_out, ldq, (T*)cache, tables, tok_seg, pos, inv_freq,
                                                           n_q, n_k, head_dim, rot_offset, rot_dims, interleaved, v_mode, page_size,
