@@ -58,7 +58,16 @@ class AttentionMixer(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(float(head_dim))
         self.position = build_part("position", position)
         self.value_from_key, self.unit_sink = bool(value_from_key), bool(unit_sink)
-        if self.value_from_key and not getattr(self.position, "takes_value_from_key", False):
+        # A rotate-half span at the start of a head of a multiple of 16 entries runs on the kernels that turn whole heads,
+        # with the head's entries reordered at bind (SpanAsWholeRotaryPosition); keys that are also values then come out
+        # of the product twice (the key rows stand in the stacked weight a second time, as the value rows), so that the
+        # fused decode product and the vectorised rotation append them as they append any values.
+        self._reordered = (position.kind == "rope_span" and not self.position.interleaved and self.position.offset == 0
+                           and head_dim % 16 == 0)
+        if self._reordered:
+            self.position = build_part("position", PartSpec("rope_span_as_whole", {
+                "head_dim": head_dim, "dims": self.position.dims, "theta": self.position.theta}))
+        elif self.value_from_key and not getattr(self.position, "takes_value_from_key", False):
             raise ValueError(f"attention: the position rule {position.kind!r} cannot append unturned keys as values")
         self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
                       "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias"}
@@ -83,6 +92,24 @@ class AttentionMixer(Mixer):
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         nm = self.names
         roles = ("q", "k") if self.value_from_key else ("q", "k", "v")
+        if self._reordered:
+            order = self.position.head_order().to(tensors[nm["q"]].device)
+
+            def rows(t: torch.Tensor, heads: int) -> torch.Tensor:          # a projection's rows (or a bias), head by head
+                return t.view(heads, self.head_dim, *t.shape[1:])[:, order].reshape(t.shape)
+
+            tensors = dict(tensors)
+            for r in roles:
+                heads = self.num_heads if r == "q" else self.num_kv_heads
+                if r != "v":                                              # values keep their order only if they are no keys
+                    tensors[nm[r]] = rows(tensors[nm[r]], heads)
+                    if self.qkv_bias:
+                        tensors[nm[r + "_bias"]] = rows(tensors[nm[r + "_bias"]], heads)
+            if self.value_from_key:
+                # the output product reads the heads in the keys' new order
+                w_o = tensors[nm["o"]]
+                tensors[nm["o"]] = w_o.view(w_o.shape[0], self.num_heads, self.head_dim)[:, :, order].reshape(w_o.shape)
+                roles = ("q", "k", "k")
         self.w_qkv = _stack([tensors[nm[r]] for r in roles])
         if self.qkv_bias:
             self.b_qkv = _stack([tensors[nm[r + "_bias"]] for r in roles])
@@ -110,7 +137,7 @@ class AttentionMixer(Mixer):
             raise RuntimeError("attention needs a paged key/value cache")
         n = x.shape[0]
         q = ctx.empty(n, self.num_heads, self.head_dim)
-        if self.value_from_key:
+        if self.value_from_key and not self._reordered:
             qk = ctx.empty(n, self.q_dim + self.kv_dim)
             ops.linear(x, self.w_qkv, self.b_qkv, qk)
             self.position.rotate_append(qk, q, cache, ctx, self.num_heads, self.num_kv_heads, self.head_dim,

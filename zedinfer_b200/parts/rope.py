@@ -42,6 +42,10 @@ class RotaryPosition(PositionEncoding):
             self._inv_freq = self.inverse_frequencies().to(device)
         return self._inv_freq
 
+    def _angles_key(self) -> tuple:
+        """What else the step's shared table of angles depends on, for rules derived from this one."""
+        return ()
+
     def rotate_append(self, qkv: torch.Tensor, q_out: torch.Tensor, cache: CallCacheView, ctx: StepContext,
                       n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool) -> None:
         if head_dim != self.head_dim:
@@ -55,7 +59,7 @@ class RotaryPosition(PositionEncoding):
     def _step_angles(self, ctx: StepContext, device: torch.device) -> torch.Tensor:
         """cos | sin of every token's angles, float32 ``[tokens, head_dim]``: made by the first layer of a step that
         asks, shared by every layer with the same theta and head size."""
-        key = ("rope_cs", self.theta, self.head_dim)
+        key = ("rope_cs", self.theta, self.head_dim) + self._angles_key()
         cs = ctx.step_cache.get(key)
         if cs is None:
             cs = torch.empty((ctx.positions.numel(), self.head_dim), dtype=torch.float32, device=device)
@@ -123,3 +127,38 @@ class SpanRotaryPosition(PositionEncoding):
     def rotate_queries(self, q: torch.Tensor, ctx: StepContext, n_heads: int) -> None:
         """In place, queries alone: ``q [tokens, n_heads * head_dim]`` (rows may be strided)."""
         ops.rotary(q, q, ctx.positions, self.table(q.device), n_heads, 0, self.head_dim, self.offset, self.dims, self.interleaved)
+
+
+@register_position("rope_span_as_whole")
+class SpanAsWholeRotaryPosition(RotaryPosition):
+    """A rotate-half rotation of the first ``dims`` entries of a head, run by the kernels that turn whole heads.
+
+    Those kernels pair entry k with k + head_dim / 2.  With the head's entries reordered as ``[first half of the span |
+    first half of the rest | second half of the span | second half of the rest]`` (:meth:`head_order`; the mixer reorders
+    the rows of its query and key weights and the columns of its output weight once, when it binds them) every pair of
+    the span is such a pair, and the pairs of the rest get the frequency 0: angle 0, cosine 1, sine 0, and ``a * 1 - b * 0``
+    is a.  Scores do not change under one reordering of queries and keys.  So the fused decode product (rotation and cache
+    append in its epilogue) and the vectorised rotation of prompts serve a partly turned head as they are."""
+
+    def __init__(self, head_dim: int, dims: int, theta: float):
+        super().__init__(head_dim, theta)
+        if dims <= 0 or dims % 2 or dims > head_dim:
+            raise ValueError(f"rope_span_as_whole: a span of {dims} entries must be even and fit a head of {head_dim}")
+        self.dims = int(dims)
+
+    def inverse_frequencies(self) -> torch.Tensor:
+        """float32: 1 / powf(theta, float(2i) / float(dims)) for the span's pairs, 0 for the others."""
+        expo = torch.arange(0, self.dims, 2, dtype=torch.float32) / torch.tensor(float(self.dims), dtype=torch.float32)
+        out = torch.zeros(self.head_dim // 2, dtype=torch.float32)
+        out[:self.dims // 2] = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float32), expo)
+        return out
+
+    def _angles_key(self) -> tuple:
+        return ("span", self.dims)
+
+    def head_order(self) -> torch.Tensor:
+        """``order[new] = old``: where each entry of a reordered head comes from."""
+        d, r = self.head_dim, self.dims
+        rest = (d - r) // 2
+        return torch.tensor(list(range(0, r // 2)) + list(range(r, r + rest)) + list(range(r // 2, r)) + list(range(r + rest, d)),
+                            dtype=torch.long)
