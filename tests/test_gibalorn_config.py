@@ -132,3 +132,8 @@ def test_plain_mechanisms_agree_with_each_other():
     assert torch.allclose(w[3], torch.full((4,), 0.2, dtype=torch.float64)) and torch.allclose(w[0], torch.tensor([0.5, 0, 0, 0], dtype=torch.float64))
     idx, wts = GP.route(torch.zeros(2, 4, dtype=torch.float64), torch.ones(5, 4, dtype=torch.float64), 2)
     assert idx.tolist() == [[0, 1], [0, 1]] and bool((wts == 0.5).all())
+    # a router's margin: how far the last chosen logit lies above the first one left out
+    h = torch.tensor([[1.0, 0.0], [0.0, 1.0]], dtype=torch.float64)
+    wr = torch.tensor([[3.0, 0.0], [1.0, 5.0], [2.5, 4.0]], dtype=torch.float64)
+    assert GP.route_margin(h, wr, 1).tolist() == [0.5, 1.0] and GP.route_margin(h, wr, 2).tolist() == [1.5, 4.0]
+    assert bool(torch.isinf(GP.route_margin(h, wr, 3)).all())
